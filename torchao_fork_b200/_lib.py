@@ -119,3 +119,56 @@ def check(code, what):
     if code != 0:
         msg = lib().ao_b200_error_string(code).decode()
         raise RuntimeError(f"libao_b200: {what} failed: {msg} (code {code})")
+
+
+# ------------------------------------------------------------------------------------------------ libao_b200_lm.so
+# Sequence-model mechanisms (include/ao_b200_lm.h).  Built on first use when it is missing or older than its sources
+# (a fresh checkout has no binaries); the core library above is not needed for it.
+LM_LIB_PATH = os.path.join(_HERE, "lib", "libao_b200_lm.so")
+DT_BF16, DT_F32 = 0, 1
+_p32 = ctypes.POINTER(ctypes.c_int)
+
+LM_SIGNATURES = {
+    "ao_lm_abi_version": [],
+    "ao_lm_embed": [_vp, _i32, _vp, _i64, _i64, _vp, _vp],
+    "ao_lm_token_shift": [_vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _vp, _vp],
+    "ao_lm_residual_norm": [_vp, _vp, _i32, _vp, _i32, _f32, _f32, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp],
+    "ao_lm_scalar_norm_rows": [_vp, _vp, _i64, _i64, _vp, _i32, _f32, _vp, _vp],
+    "ao_lm_latent_prep": [_vp, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _f32, _i32, _vp, _vp, _vp, _vp,
+                          _vp, _i64, _vp, _vp, _vp, _vp],
+    "ao_lm_latent_attention_plan": [_i32, _p32],
+    "ao_lm_latent_attention_workspace_bytes": [_i64, _i32, _i32, _i32],
+    "ao_lm_latent_attention": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp,
+                               _i32, _i32, _vp, _i64, _vp, _vp],
+    "ao_lm_router_topk": [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp],
+    "ao_lm_glu_act": [_vp, _i32, _i64, _i64, _f32, _f32, _vp, _vp],
+    "ao_lm_expert_gate_up": [_vp, _vp, _vp, _i32, _vp, _i64, _i32, _i64, _i64, _i64, _f32, _f32, _vp, _vp],
+    "ao_lm_expert_down": [_vp, _vp, _i32, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _vp, _vp],
+    "ao_lm_gather_rows": [_vp, _i32, _vp, _i32, _i64, _i64, _vp, _vp],
+    "ao_lm_scatter_add_rows": [_vp, _i32, _vp, _vp, _i32, _i64, _i64, _vp, _vp],
+    "ao_lm_add_cast": [_vp, _i32, _i64, _vp, _vp],
+    "ao_lm_argmax": [_vp, _i64, _i64, _i64, _vp, _vp],
+}
+_LM_RESTYPES = {"ao_lm_latent_attention_workspace_bytes": _i64}
+_lm = None
+_LM_ERRORS = {1: "invalid argument", 2: "unsupported shape", 3: "CUDA launch failed", 4: "workspace too small"}
+
+
+def lm():
+    """The loaded libao_b200_lm.so; compiles it first if the checkout has no current build.  No fallback path."""
+    global _lm
+    if _lm is None:
+        from . import build as _build
+        _build.build(target="lm")
+        handle = ctypes.CDLL(LM_LIB_PATH)
+        for name, argtypes in LM_SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = _LM_RESTYPES.get(name, _i32)
+        _lm = handle
+    return _lm
+
+
+def lm_check(code, what):
+    if code != 0:
+        raise RuntimeError(f"libao_b200_lm: {what} failed: {_LM_ERRORS.get(code, 'error')} (code {code})")

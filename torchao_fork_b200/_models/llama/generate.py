@@ -50,9 +50,14 @@ class Generator:
                  kv_cache_quantization: bool = False):
         self.model = model
         self.batch_size = batch_size
-        dev = model.tok_embeddings.weight.device
+        dev = model.device if hasattr(model, "make_decode_engine") else model.tok_embeddings.weight.device
         model.setup_caches(batch_size, max_seq_length, device=dev, kv_cache_quantization=kv_cache_quantization)
-        self.engine = DecodeEngine(model, batch_size, temperature, top_k, tp=tp, mega=mega)
+        if hasattr(model, "make_decode_engine"):
+            # a model family with its own step function brings the decode engine that wraps it (same surface)
+            assert tp is None, "tensor parallel decode exists for the Llama family only"
+            self.engine = model.make_decode_engine(batch_size, temperature, top_k)
+        else:
+            self.engine = DecodeEngine(model, batch_size, temperature, top_k, tp=tp, mega=mega)
         if use_graph:
             self.engine.capture()
         self.sampling = dict(temperature=temperature, top_k=top_k)
@@ -200,6 +205,11 @@ def generate(model: Transformer, prompt: torch.Tensor, max_new_tokens: int, batc
 def _load_model(checkpoint_path, device, precision):
     """reference: generate.py:241-253.  Also loads what `--save` wrote: a state_dict whose linear weights are already
     quantized tensor subclasses (AffineQuantizedTensor / Int4Tensor) — `assign=True` keeps them as they are."""
+    from ..checkpoint import is_checkpoint_folder
+    if is_checkpoint_folder(checkpoint_path):
+        # config.json + model.safetensors: the architecture named in config.json picks the model family
+        from ..registry import load_checkpoint_folder
+        return load_checkpoint_folder(checkpoint_path, device, precision)
     checkpoint = torch.load(str(checkpoint_path), mmap=True, weights_only=True, map_location="cpu")
     if "model" in checkpoint and "stories" in str(checkpoint_path):
         checkpoint = checkpoint["model"]
@@ -211,6 +221,9 @@ def _load_model(checkpoint_path, device, precision):
 
 def _random_init_model(name, device, precision):
     """No checkpoints exist offline: the architecture `name` with seeded random weights (what bench.py measures)."""
+    from ..bitipel import Bitipel, bitipel_configs
+    if name in bitipel_configs:
+        return Bitipel.from_name(name, device, precision)
     torch.manual_seed(1234)
     old = torch.get_default_dtype()
     torch.set_default_dtype(precision)
@@ -228,6 +241,8 @@ def apply_quantization(model, quantization: Optional[str]):
     from ... import Int4WeightOnlyConfig, Int8WeightOnlyConfig, quantize_
     if not quantization:
         return model
+    if not isinstance(model, Transformer):
+        raise NotImplementedError(f"-q {quantization}: weight-only quantization is wired to the Llama family's linears")
     if "int8wo" in quantization:
         quantize_(model, Int8WeightOnlyConfig())
     elif "int4wo" in quantization:
@@ -243,6 +258,9 @@ def apply_quantization(model, quantization: Optional[str]):
 def get_model_size_in_bytes(model, ignore_embeddings=False):
     """reference: torchao/utils.py:234-262 — bytes of every parameter / buffer, tensor subclasses counted by their inner
     tensors."""
+    if hasattr(model, "weight_bytes"):
+        return model.weight_bytes(ignore_embeddings)
+
     def nbytes(t):
         if hasattr(t, "__tensor_flatten__"):
             names, _ = t.__tensor_flatten__()
@@ -273,7 +291,7 @@ def main(prefill_size: Optional[int] = None, prompt="Hello, my name is", num_sam
     tokenizer = None
     if checkpoint_path is not None:
         checkpoint_path = Path(checkpoint_path)
-        assert checkpoint_path.is_file(), checkpoint_path
+        assert checkpoint_path.is_file() or checkpoint_path.is_dir(), checkpoint_path
         model = _load_model(checkpoint_path, device, precision)
         tok_path = checkpoint_path.parent / "tokenizer.model"
         if tok_path.is_file():
@@ -374,7 +392,8 @@ if __name__ == "__main__":
     parser.add_argument("--batch_size", type=int, default=1, help="Batch size to benchmark with")
     parser.add_argument("--top_k", type=int, default=200, help="Top-k for sampling.")
     parser.add_argument("--temperature", type=float, default=0.8, help="Temperature for sampling.")
-    parser.add_argument("--checkpoint_path", type=Path, default=None, help="Model checkpoint path.")
+    parser.add_argument("--checkpoint_path", type=Path, default=None,
+                        help="Model checkpoint path: a gpt-fast model.pth, or a folder with config.json + model.safetensors")
     parser.add_argument("--random_init", type=str, default=None,
                         help="model name (e.g. Llama-3-8B): seeded random weights instead of a checkpoint (no checkpoints offline)")
     parser.add_argument("-q", "--quantization", type=str, help="int8wo, int4wo-<groupsize>, int4wo-<groupsize>-hqq")

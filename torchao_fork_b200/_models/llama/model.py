@@ -81,55 +81,7 @@ transformer_configs = {
 }
 
 
-class KVCache(nn.Module):
-    """reference: model.py:166-192.  [B][n_local_heads][S][head_dim]"""
-
-    def __init__(self, max_batch_size, max_seq_length, n_heads, head_dim, dtype=torch.bfloat16):
-        super().__init__()
-        shape = (max_batch_size, n_heads, max_seq_length, head_dim)
-        self.register_buffer("k_cache", torch.zeros(shape, dtype=dtype))
-        self.register_buffer("v_cache", torch.zeros(shape, dtype=dtype))
-
-    def update(self, input_pos, k_val, v_val):
-        assert input_pos.shape[0] == k_val.shape[2]
-        self.k_cache[:, :, input_pos] = k_val
-        self.v_cache[:, :, input_pos] = v_val
-        return self.k_cache, self.v_cache
-
-
-class AffineQuantizedKVCache(nn.Module):
-    """reference: model.py:198-240.  int8 rows [B][n_local_heads][S][head_dim] + one scale per row
-    [B][n_local_heads][S][1]; update() returns the dequantized caches with the positions just written replaced by the
-    unquantized values.  (Decode steps do not call update(): csrc/decode_attn_q8.cu does the same thing for the new
-    row inside the attention launch and never materialises the dequantized cache.)"""
-
-    def __init__(self, max_batch_size, max_seq_length, n_heads, head_dim, scale_dtype=torch.bfloat16):
-        super().__init__()
-        cache_shape = (max_batch_size, n_heads, max_seq_length, head_dim)
-        scale_shape = (max_batch_size, n_heads, max_seq_length, 1)
-        self.register_buffer("k_cache", torch.zeros(cache_shape, dtype=torch.int8))
-        self.register_buffer("v_cache", torch.zeros(cache_shape, dtype=torch.int8))
-        self.register_buffer("k_cache_scale", torch.ones(scale_shape, dtype=scale_dtype))
-        self.register_buffer("v_cache_scale", torch.ones(scale_shape, dtype=scale_dtype))
-
-    def update(self, input_pos, k_val, v_val):
-        from ...quantization.utils import _quantize_activation_per_token_absmax
-        q_k_val, k_scale = _quantize_activation_per_token_absmax(k_val)
-        self.k_cache[:, :, input_pos] = q_k_val
-        self.k_cache_scale[:, :, input_pos] = k_scale.unsqueeze(-1)
-        k_out = self.k_cache * self.k_cache_scale
-        k_out[:, :, input_pos] = k_val
-        q_v_val, v_scale = _quantize_activation_per_token_absmax(v_val)
-        self.v_cache[:, :, input_pos] = q_v_val
-        self.v_cache_scale[:, :, input_pos] = v_scale.unsqueeze(-1)
-        v_out = self.v_cache * self.v_cache_scale
-        v_out[:, :, input_pos] = v_val
-        return k_out, v_out
-
-    @classmethod
-    def from_float(cls, kv_cache):
-        max_batch_size, n_heads, max_seq_length, head_dim = kv_cache.k_cache.shape
-        return cls(max_batch_size, max_seq_length, n_heads, head_dim, kv_cache.k_cache.dtype)
+from ..cache import AffineQuantizedKVCache, KVCache  # noqa: E402,F401  (the cache classes of every model family live together)
 
 
 class RMSNorm(nn.Module):

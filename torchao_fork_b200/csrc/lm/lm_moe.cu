@@ -1,0 +1,184 @@
+// Mixture of clipped-GLU experts: fp32 softmax router with top-k choice, and the expert products for a handful of
+// tokens (decode, short portions) as matrix-vector kernels that read the expert index from device memory — no host
+// round trip, so the step can be captured into a CUDA graph.  Prompt-sized batches sort their rows by expert and use
+// the gather / scatter kernels at the end of this file around library GEMMs.
+#include "lm_common.cuh"
+
+using namespace lm;
+
+namespace {
+
+constexpr int kWarps = 8;
+
+// one CTA per token: E dot products (a warp each, round robin), then warp 0 does softmax + top-k
+template <typename T>
+__global__ void router_topk_kernel(const T* __restrict__ h, const T* __restrict__ wr, int64_t W, int E, int top,
+                                   int32_t* __restrict__ idx, float* __restrict__ weight) {
+  extern __shared__ float sm[];
+  float* xs = sm;          // [W]
+  float* z = sm + W;       // [E]
+  const int64_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) xs[w] = ldf(h + t * W + w);
+  __syncthreads();
+  const bool vec = rows_vectorizable<T>(wr, W);
+  for (int e = warp; e < E; e += kWarps) {
+    const float v = warp_dot(wr + (int64_t)e * W, xs, W, lane, vec);
+    if (lane == 0) z[e] = v;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
+  den = warp_sum(den);
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = E;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) best = z[e], at = e;          // ascending e: the lowest index wins inside a lane
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
+    }
+    if (lane == 0) {
+      idx[t * top + k] = at;
+      weight[t * top + k] = expf(best - mx) / den;
+    }
+    __syncwarp();
+    if (lane == 0 && at < E) z[at] = -INFINITY;
+    __syncwarp();
+  }
+}
+
+// grid (ceil(ff / 8), pairs): a warp computes one row of both projections of its pair's expert
+template <typename T>
+__global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ wg, const T* __restrict__ wu,
+                                      const int32_t* __restrict__ idx, int top, int64_t W, int64_t ff,
+                                      int64_t expert_stride, float limit, float alpha, T* __restrict__ y) {
+  extern __shared__ float xs[];   // [W]
+  const int64_t p = blockIdx.y, t = p / top;
+  const int64_t e = idx ? idx[p] : 0;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) xs[w] = ldf(h + t * W + w);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t f = (int64_t)blockIdx.x * kWarps + warp;
+  if (f >= ff) return;
+  const bool vec = rows_vectorizable<T>(wg, W) && rows_vectorizable<T>(wu, W);
+  const float a = warp_dot(wg + e * expert_stride + f * W, xs, W, lane, vec);
+  const float b = warp_dot(wu + e * expert_stride + f * W, xs, W, lane, vec);
+  if (lane == 0) {
+    // the projections' outputs are activations of the storage type: round them as a GEMM would
+    T ra, rb;
+    stf(&ra, a);
+    stf(&rb, b);
+    const float g = fminf(ldf(&ra), limit);
+    const float u = fminf(fmaxf(ldf(&rb), -limit), limit);
+    stf(y + p * ff + f, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+// grid (ceil(W / 8), n): a warp computes one output coordinate of its token over the token's `top` experts
+template <typename T>
+__global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict__ wd, const int32_t* __restrict__ idx,
+                                   const float* __restrict__ weight, int top, int64_t W, int64_t ff, int accumulate,
+                                   float* __restrict__ out) {
+  extern __shared__ float ys[];   // [top][ff]
+  const int64_t t = blockIdx.y;
+  for (int64_t i = threadIdx.x; i < top * ff; i += blockDim.x) ys[i] = ldf(y + t * top * ff + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
+  if (w >= W) return;
+  const bool vec = rows_vectorizable<T>(wd, ff);
+  float acc = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int64_t e = idx ? idx[t * top + k] : 0;
+    const float d = warp_dot(wd + (e * W + w) * ff, ys + (int64_t)k * ff, ff, lane, vec);
+    T rd;
+    stf(&rd, d);                  // an expert's output is an activation of the storage type
+    acc = fmaf(weight ? weight[t * top + k] : 1.f, ldf(&rd), acc);
+  }
+  if (lane == 0) out[t * W + w] = (accumulate ? out[t * W + w] : 0.f) + acc;
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ h, const int64_t* __restrict__ src, int top, int64_t W, T* __restrict__ xs) {
+  const int64_t i = blockIdx.x, t = src[i] / top;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) xs[i * W + w] = h[t * W + w];
+}
+
+template <typename T>
+__global__ void scatter_add_rows_kernel(const T* __restrict__ y, const int64_t* __restrict__ src, const float* __restrict__ weight,
+                                        int top, int64_t W, float* __restrict__ out) {
+  const int64_t i = blockIdx.x, p = src[i], t = p / top;
+  const float k = weight[p];
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) atomicAdd(out + t * W + w, k * ldf(y + i * W + w));
+}
+
+}  // namespace
+
+extern "C" int ao_lm_router_topk(const void* h, const void* w_router, int dt, int64_t n, int64_t width, int E, int top,
+                                 int32_t* idx, float* weight, void* stream) {
+  LM_CHECK_ARG(h && w_router && idx && weight && n > 0 && width > 0 && E > 0 && top > 0 && top <= E);
+  const size_t smem = (size_t)(width + E) * sizeof(float);
+  if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  LM_DISPATCH(dt, {
+    auto kern = router_topk_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    kern<<<(unsigned)n, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_router), width,
+                                                               E, top, idx, weight);
+  });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_expert_gate_up(const void* h, const void* w_gate, const void* w_up, int dt, const int32_t* idx, int64_t n,
+                                    int top, int64_t width, int64_t ff, int64_t expert_stride, float limit, float alpha, void* y,
+                                    void* stream) {
+  LM_CHECK_ARG(h && w_gate && w_up && y && n > 0 && top > 0 && width > 0 && ff > 0 && n * top <= 65535);
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((ff + kWarps - 1) / kWarps), (unsigned)(n * top));
+  LM_DISPATCH(dt, {
+    auto kern = expert_gate_up_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    kern<<<grid, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_gate),
+                                                        static_cast<const T*>(w_up), idx, top, width, ff, expert_stride, limit, alpha,
+                                                        static_cast<T*>(y));
+  });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_expert_down(const void* y, const void* w_down, int dt, const int32_t* idx, const float* weight, int64_t n,
+                                 int top, int64_t width, int64_t ff, int accumulate, float* out, void* stream) {
+  LM_CHECK_ARG(y && w_down && out && n > 0 && top > 0 && width > 0 && ff > 0 && n <= 65535);
+  const size_t smem = (size_t)top * ff * sizeof(float);
+  if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((width + kWarps - 1) / kWarps), (unsigned)n);
+  LM_DISPATCH(dt, {
+    auto kern = expert_down_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    kern<<<grid, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(y), static_cast<const T*>(w_down), idx, weight, top,
+                                                        width, ff, accumulate, out);
+  });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_gather_rows(const void* h, int dt, const int64_t* src, int top, int64_t m, int64_t width, void* xs,
+                                 void* stream) {
+  LM_CHECK_ARG(h && src && xs && top > 0 && m > 0 && width > 0);
+  LM_DISPATCH(dt, gather_rows_kernel<T><<<(unsigned)m, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(h), src, top, width,
+                                                                                    static_cast<T*>(xs)));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_scatter_add_rows(const void* y, int dt, const int64_t* src, const float* weight, int top, int64_t m,
+                                      int64_t width, float* out, void* stream) {
+  LM_CHECK_ARG(y && src && weight && out && top > 0 && m > 0 && width > 0);
+  LM_DISPATCH(dt, scatter_add_rows_kernel<T><<<(unsigned)m, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(y), src, weight,
+                                                                                         top, width, out));
+  return lm_launch_status();
+}

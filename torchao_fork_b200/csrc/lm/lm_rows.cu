@@ -1,0 +1,254 @@
+// Row-wise kernels of the fp32 residual stream: embedding gather, token shift, residual add with a scalar-weight RMS
+// norm (+ token-shift memory, + depth-weighted average of the layer results, + storage-type copy), latent-attention
+// projection split (latent norm, rotary, gate), clipped-GLU activation, greedy argmax.  One CTA per token row.
+#include "lm_common.cuh"
+
+using namespace lm;
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int64_t* __restrict__ tok, int64_t W, float* __restrict__ x) {
+  const int64_t t = blockIdx.x;
+  const T* row = table + tok[t] * W;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) x[t * W + w] = ldf(row + w);
+}
+
+template <typename T>
+__global__ void token_shift_kernel(const float* __restrict__ x, const T* __restrict__ mu, const float* __restrict__ state,
+                                   const int32_t* __restrict__ slot, const int32_t* __restrict__ pos, int64_t W,
+                                   T* __restrict__ h) {
+  const int64_t t = blockIdx.x;
+  const int p = pos[t], s = slot[t];
+  const float* prev = nullptr;
+  if (p > 0) prev = (t > 0 && slot[t - 1] == s && pos[t - 1] == p - 1) ? x + (t - 1) * W : state + (int64_t)s * W;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+    const float v = x[t * W + w];
+    const float pv = prev ? prev[w] : 0.f;
+    stf(h + t * W + w, v + (pv - v) * ldf(mu + w));
+  }
+}
+
+template <typename T, typename TY>
+__global__ void residual_norm_kernel(const float* __restrict__ x_in, const TY* __restrict__ y, const T* __restrict__ g,
+                                     float mult, float eps, int64_t n, int64_t W, float* __restrict__ x_out,
+                                     float* __restrict__ state, const int32_t* __restrict__ slot,
+                                     const float* __restrict__ streams, int n_streams, int64_t stream_stride,
+                                     const T* __restrict__ coef, float* __restrict__ avg_out, T* __restrict__ cast_out) {
+  __shared__ float scratch[33];
+  const int64_t t = blockIdx.x;
+  const TY* yr = y + t * W;
+  float ss = 0.f;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+    const float v = ldf(yr + w);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float k = mult * ldf(g) / sqrtf(ss / (float)W + eps);
+  const bool save = state && (t == n - 1 || slot[t + 1] != slot[t]);
+  float* st = save ? state + (int64_t)slot[t] * W : nullptr;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+    const float xi = x_in[t * W + w];
+    if (st) st[w] = xi;
+    float v = fmaf(k, ldf(yr + w), xi);
+    x_out[t * W + w] = v;
+    if (streams) {
+      float a = ldf(coef + n_streams) * v;
+      for (int j = n_streams - 1; j >= 0; --j) a = fmaf(ldf(coef + j), streams[j * stream_stride + t * W + w], a);
+      avg_out[t * W + w] = a;
+      v = a;
+    }
+    if (cast_out) stf(cast_out + t * W + w, v);
+  }
+}
+
+template <typename T>
+__global__ void scalar_norm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, int64_t W,
+                                        const T* __restrict__ g, float eps, T* __restrict__ out) {
+  __shared__ float scratch[33];
+  const int64_t i = blockIdx.x;
+  const float* xr = x + (rows ? (int64_t)rows[i] : i) * W;
+  float ss = 0.f;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) ss = fmaf(xr[w], xr[w], ss);
+  ss = block_sum(ss, scratch);
+  const float k = ldf(g) / sqrtf(ss / (float)W + eps);
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) stf(out + i * W + w, xr[w] * k);
+}
+
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t ld, int64_t n, int H, int dn, int dr, int R,
+                                   int64_t q_off, int64_t kv_off, int64_t g_off, const T* __restrict__ c_norm, float eps,
+                                   int rot_dims, const float* __restrict__ inv_freq, const int32_t* __restrict__ slot,
+                                   const int32_t* __restrict__ pos, T* __restrict__ c_cache, T* __restrict__ kr_cache,
+                                   int64_t S, T* __restrict__ qn, float* __restrict__ qr, float* __restrict__ gate) {
+  __shared__ float scratch[33];
+  const int64_t t = blockIdx.x;
+  const T* row = proj + t * ld;
+  const int p = pos[t];
+  const float fp = (float)p;
+  const int half = rot_dims / 2;
+  // unrotated query parts, head-major
+  for (int i = threadIdx.x; i < H * dn; i += blockDim.x) {
+    const int h = i / dn, d = i - h * dn;
+    qn[((int64_t)h * n + t) * dn + d] = row[q_off + (int64_t)h * (dn + dr) + d];
+  }
+  // rotated query parts: one thread per pair, then the tail that is not rotated
+  for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const T* q = row + q_off + (int64_t)h * (dn + dr) + dn;
+    float sn, cs;
+    sincosf(fp * inv_freq[j], &sn, &cs);
+    const float u = ldf(q + 2 * j), v = ldf(q + 2 * j + 1);
+    float* o = qr + (t * H + h) * dr;
+    o[2 * j] = u * cs - v * sn;
+    o[2 * j + 1] = v * cs + u * sn;
+  }
+  for (int i = threadIdx.x; i < H * (dr - 2 * half); i += blockDim.x) {
+    const int h = i / (dr - 2 * half), d = 2 * half + (i - h * (dr - 2 * half));
+    qr[(t * H + h) * dr + d] = ldf(row + q_off + (int64_t)h * (dn + dr) + dn + d);
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) gate[t * H + h] = 1.f / (1.f + expf(-ldf(row + g_off + h)));
+  if (kv_off < 0) return;   // uniform over the block
+  const T* kv = row + kv_off;
+  const int64_t at = (int64_t)slot[t] * S + p;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const float v = ldf(kv + i);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float k = 1.f / sqrtf(ss / (float)R + eps);
+  for (int i = threadIdx.x; i < R; i += blockDim.x) stf(c_cache + at * R + i, ldf(kv + i) * k * ldf(c_norm + i));
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float sn, cs;
+    sincosf(fp * inv_freq[j], &sn, &cs);
+    const float u = ldf(kv + R + 2 * j), v = ldf(kv + R + 2 * j + 1);
+    stf(kr_cache + at * dr + 2 * j, u * cs - v * sn);
+    stf(kr_cache + at * dr + 2 * j + 1, v * cs + u * sn);
+  }
+  for (int d = 2 * half + threadIdx.x; d < dr; d += blockDim.x) kr_cache[at * dr + d] = kv[R + d];
+}
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, int64_t n, int64_t ff, float limit, float alpha, T* __restrict__ y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * ff) return;
+  const int64_t t = i / ff, f = i - t * ff;
+  const float g = fminf(ldf(gu + t * 2 * ff + f), limit);
+  const float u = fminf(fmaxf(ldf(gu + t * 2 * ff + ff + f), -limit), limit);
+  stf(y + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+template <typename T>
+__global__ void add_cast_kernel(const T* __restrict__ b, int64_t count, float* __restrict__ a) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) a[i] += ldf(b + i);
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int64_t V, int64_t* __restrict__ out) {
+  __shared__ float bv[32];
+  __shared__ int64_t bi[32];
+  const float* row = logits + blockIdx.x * ld;
+  float best = -INFINITY;
+  int64_t at = V;
+  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < at)) best = v, at = i;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, at, o);
+    if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
+  }
+  if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = at;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (bv[w] > best || (bv[w] == best && bi[w] < at)) best = bv[w], at = bi[w];
+    out[blockIdx.x] = at < V ? at : 0;
+  }
+}
+
+}  // namespace
+
+extern "C" int ao_lm_abi_version(void) { return 1; }
+
+extern "C" int ao_lm_embed(const void* table, int dt, const int64_t* tok, int64_t n, int64_t width, float* x, void* stream) {
+  LM_CHECK_ARG(table && tok && x && n > 0 && width > 0);
+  LM_DISPATCH(dt, embed_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(static_cast<const T*>(table), tok, width, x));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_token_shift(const float* x, const void* mu, int dt, const float* state, const int32_t* slot,
+                                 const int32_t* pos, int64_t n, int64_t width, void* h, void* stream) {
+  LM_CHECK_ARG(x && mu && state && slot && pos && h && n > 0 && width > 0);
+  LM_DISPATCH(dt, token_shift_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+                      x, static_cast<const T*>(mu), state, slot, pos, width, static_cast<T*>(h)));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_residual_norm(const float* x_in, const void* y, int y_dt, const void* g, int dt, float mult, float eps,
+                                   int64_t n, int64_t width, float* x_out, float* state, const int32_t* slot,
+                                   const float* streams, int n_streams, int64_t stream_stride, const void* coef,
+                                   float* avg_out, void* cast_out, void* stream) {
+  LM_CHECK_ARG(x_in && y && g && x_out && n > 0 && width > 0);
+  LM_CHECK_ARG((!state || slot) && (!streams || (coef && avg_out && n_streams >= 0)));
+  LM_DISPATCH(dt, {
+    if (y_dt == AO_LM_F32)
+      residual_norm_kernel<T, float><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+          x_in, static_cast<const float*>(y), static_cast<const T*>(g), mult, eps, n, width, x_out, state, slot, streams,
+          n_streams, stream_stride, static_cast<const T*>(coef), avg_out, static_cast<T*>(cast_out));
+    else if (y_dt == dt)
+      residual_norm_kernel<T, T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+          x_in, static_cast<const T*>(y), static_cast<const T*>(g), mult, eps, n, width, x_out, state, slot, streams,
+          n_streams, stream_stride, static_cast<const T*>(coef), avg_out, static_cast<T*>(cast_out));
+    else
+      return AO_B200_ERR_INVALID_ARG;
+  });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_scalar_norm_rows(const float* x, const int32_t* rows, int64_t m, int64_t width, const void* g, int dt,
+                                      float eps, void* out, void* stream) {
+  LM_CHECK_ARG(x && g && out && m > 0 && width > 0);
+  LM_DISPATCH(dt, scalar_norm_rows_kernel<T><<<(unsigned)m, kRowThreads, 0, lm_stream(stream)>>>(
+                      x, rows, width, static_cast<const T*>(g), eps, static_cast<T*>(out)));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_latent_prep(const void* proj, int dt, int64_t ld, int64_t n, int H, int dn, int dr, int R, int64_t q_off,
+                                 int64_t kv_off, int64_t g_off, const void* c_norm, float eps, int rot_dims,
+                                 const float* inv_freq, const int32_t* slot, const int32_t* pos, void* c_cache,
+                                 void* kr_cache, int64_t S, void* qn, float* qr, float* gate, void* stream) {
+  LM_CHECK_ARG(proj && slot && pos && qn && qr && gate && n > 0 && H > 0 && dn >= 0 && dr >= 0 && R > 0);
+  LM_CHECK_ARG(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq));
+  LM_CHECK_ARG(kv_off < 0 || (c_norm && c_cache && kr_cache && S > 0));
+  LM_DISPATCH(dt, latent_prep_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+                      static_cast<const T*>(proj), ld, n, H, dn, dr, R, q_off, kv_off, g_off, static_cast<const T*>(c_norm), eps,
+                      rot_dims, inv_freq, slot, pos, static_cast<T*>(c_cache), static_cast<T*>(kr_cache), S,
+                      static_cast<T*>(qn), qr, gate));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_glu_act(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, void* y, void* stream) {
+  LM_CHECK_ARG(gu && y && n > 0 && ff > 0);
+  const unsigned grid = (unsigned)((n * ff + 255) / 256);
+  LM_DISPATCH(dt, glu_act_kernel<T><<<grid, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(gu), n, ff, limit, alpha,
+                                                                         static_cast<T*>(y)));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_add_cast(const void* b, int dt, int64_t count, float* a_inout, void* stream) {
+  LM_CHECK_ARG(b && a_inout && count > 0);
+  const unsigned grid = (unsigned)((count + 255) / 256);
+  LM_DISPATCH(dt, add_cast_kernel<T><<<grid, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(b), count, a_inout));
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_argmax(const float* logits, int64_t ld, int64_t B, int64_t V, int64_t* out, void* stream) {
+  LM_CHECK_ARG(logits && out && B > 0 && V > 0 && ld >= V);
+  argmax_kernel<<<(unsigned)B, 256, 0, lm_stream(stream)>>>(logits, ld, V, out);
+  return lm_launch_status();
+}
