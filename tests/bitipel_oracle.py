@@ -11,6 +11,14 @@ import math
 import torch
 
 F64 = torch.float64
+# When set, every value that a bfloat16 implementation stores in bfloat16 (inputs and results of matrix products,
+# activations, cached rows) is rounded to bfloat16 here as well.  The distance between that run and the exact one is
+# the size of rounding noise for a given model and input: tests bound a bfloat16 run by a small multiple of it.
+ROUND_BF16 = False
+
+
+def _r(x):
+    return x.to(torch.bfloat16).to(F64) if ROUND_BF16 else x
 
 
 def unit_rms(x, eps):
@@ -64,9 +72,9 @@ def latent_kv(h, pos, w, pre, mx, eps):
     """The two things a latent-attention layer with its own down projection stores per token: the normed latent
     c [T][R] and the rotated key part shared by all heads kr [T][dr]."""
     R, dr = mx["kv_rank"], mx["rot_dim"]
-    d = h @ w[pre + "dkv"].to(F64).T
-    c = vector_norm(d[:, :R], w[pre + "dkv.norm"].to(F64), eps)
-    kr = rotate_pairs(d[:, R:R + dr], pos, mx["rot"]["base"], mx["rot"]["dims"])
+    d = _r(h @ w[pre + "dkv"].to(F64).T)
+    c = _r(vector_norm(d[:, :R], w[pre + "dkv.norm"].to(F64), eps))
+    kr = _r(rotate_pairs(d[:, R:R + dr], pos, mx["rot"]["base"], mx["rot"]["dims"]))
     return c, kr
 
 
@@ -76,27 +84,27 @@ def latent_attention(h, pos, c_all, kr_all, w, pre, mx):
     from the latent; softmax with a per-head sink; a per-head sigmoid gate read from h; then the output projection."""
     T = h.shape[0]
     H, dn, dr, dv, R = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
-    q = (h @ w[pre + "q"].to(F64).T).view(T, H, dn + dr)
+    q = _r(h @ w[pre + "q"].to(F64).T).view(T, H, dn + dr)
     qn = q[..., :dn]
     qr = rotate_pairs(q[..., dn:], pos, mx["rot"]["base"], mx["rot"]["dims"])
     S = c_all.shape[0]
-    kn = (c_all @ w[pre + "uk"].to(F64).T).view(S, H, dn)
-    v = (c_all @ w[pre + "uv"].to(F64).T).view(S, H, dv)
+    kn = _r(c_all @ w[pre + "uk"].to(F64).T).view(S, H, dn)
+    v = _r(c_all @ w[pre + "uv"].to(F64).T).view(S, H, dv)
     s = (torch.einsum("thd,shd->hts", qn, kn) + torch.einsum("thd,sd->hts", qr, kr_all)) * mx["scale"]
     seen = torch.arange(S).view(1, 1, S) <= pos.view(1, T, 1)
     s = s.masked_fill(~seen, -math.inf)
     p = sink_softmax(s, w[pre + "sink"].to(F64).view(H, 1, 1))
     o = torch.einsum("hts,shd->thd", p, v)
-    gate = torch.sigmoid(h @ w[pre + "g"].to(F64).T)              # [T][H]
-    o = o * gate.unsqueeze(-1)
-    return o.reshape(T, H * dv) @ w[pre + "o"].to(F64).T
+    gate = torch.sigmoid(_r(h @ w[pre + "g"].to(F64).T))          # [T][H]
+    o = _r(o * gate.unsqueeze(-1))
+    return _r(o.reshape(T, H * dv) @ w[pre + "o"].to(F64).T)
 
 
 def clipped_glu_expert(h, w, pre, limit):
     """g = min(G h, limit), u = clamp(U h, +-limit), y = g sigmoid(1.702 g) (u + 1), out = D y."""
-    g = torch.clamp(h @ w[pre + "gate"].to(F64).T, max=limit)
-    u = torch.clamp(h @ w[pre + "up"].to(F64).T, -limit, limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[pre + "down"].to(F64).T
+    g = torch.clamp(_r(h @ w[pre + "gate"].to(F64).T), max=limit)
+    u = torch.clamp(_r(h @ w[pre + "up"].to(F64).T), -limit, limit)
+    return _r(_r(g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[pre + "down"].to(F64).T)
 
 
 def route(h, w_router, top):
@@ -108,6 +116,7 @@ def route(h, w_router, top):
 def mixture(h, w, pre, mlp):
     """Routed experts weighted by their scores, plus a shared expert for every token."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
+    h = _r(h)
     wt, idx = route(h, w[pre + "router"], top)
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F64)
     for e in range(E):
@@ -134,7 +143,7 @@ def forward(cfg, w, tokens, return_layers=False):
     for i, layer in enumerate(cfg["layers"]):
         assert layer["type"] == "latent_attention"
         mx, pre = layer["mixer"], f"l{i}."
-        h = token_shift(x, w[pre + "shift"].to(F64), torch.zeros(x.shape[1], dtype=F64))
+        h = _r(token_shift(x, w[pre + "shift"].to(F64), torch.zeros(x.shape[1], dtype=F64)))
         if "kv_from" in mx:
             c, kr = kv[mx["kv_from"]]
         else:
@@ -147,8 +156,20 @@ def forward(cfg, w, tokens, return_layers=False):
         streams.append(x)
         x = depth_average(streams, w[pre + "dwa"].to(F64))
         after.append(x)
-    logits = scalar_norm(x, w["final.norm"].to(F64), eps) @ w["head"].to(F64).T
+    logits = _r(scalar_norm(x, w["final.norm"].to(F64), eps)) @ w["head"].to(F64).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def rounding_noise(cfg, w, tokens, measure):
+    """measure(run with bfloat16 roundings, exact run): how far rounding alone moves the logits of this input."""
+    global ROUND_BF16
+    exact = forward(cfg, w, tokens)
+    ROUND_BF16 = True
+    try:
+        rounded = forward(cfg, w, tokens)
+    finally:
+        ROUND_BF16 = False
+    return measure(rounded, exact)
 
 
 def greedy(cfg, w, prompt, n_new):
