@@ -592,7 +592,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)  # reference: 200 new tokens per sample (generate.py:264)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-int4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama3-8b-int4", choices=sorted(WORKLOADS) + ["bitipel-layers"],
+                    help="bitipel-layers: prefill / decode of Bitipel layers at real sizes beside the Llama family at equal size "
+                         "(benchmarks/bitipel_bench.py; its own JSON line, not the headline metric)")
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--temperature", type=float, default=0.8)
     ap.add_argument("--top-k", type=int, default=200)
@@ -600,6 +602,11 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=25.0, help="reference arm: stop timing tokens after this many seconds")
     ap.add_argument("--no-reference-gpu", action="store_true")
     args = ap.parse_args()
+    if args.workload == "bitipel-layers":
+        assert args.impl == "b200" and args.gpus == 1, "bitipel-layers is a one-GPU measurement of this repo's kernels"
+        from benchmarks import bitipel_bench
+        emit(bitipel_bench.run())
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
