@@ -108,7 +108,7 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     res = {"roofline_source": src, "hbm_gbs": hbm, "bf16_tflops": tf}
     bf = dict(dtype=torch.bfloat16, device=dev)
     tt = ctypes.c_int()
-    L.ao_lm_latent_attention_plan(H, ctypes.byref(tt))
+    L.ao_lm_latent_attention_plan(0, H, R, dr, ctypes.byref(tt))
 
     def attention(n, first_pos, n_split):
         S = first_pos + n
@@ -142,8 +142,7 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     res["llama_sdpa_prefill"] = {"tokens": n, "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 2),
                                  "frac_bf16_tensor_peak": round(flops / ms / 1e9 / tf, 4)}
     # one decoded token: the cached rows of the context are read once
-    groups = max(1, -(-((H + 3) // 4) // 8))
-    ns = max(1, min(-(-(decode_ctx + 1) // 64), -(-2 * 148 // groups), 64))
+    ns = max(1, min(-(-(decode_ctx + 1) // 32), -(-2 * 148 // -(-H // 16)), 64))   # what the decode engine picks
     ms = attention(1, decode_ctx, ns)
     byts = (decode_ctx + 1) * (R + dr) * 2
     res["latent_attention_decode"] = {"context": decode_ctx, "splits": ns, "us": round(ms * 1e3, 2), "cache_bytes": byts,

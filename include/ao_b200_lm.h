@@ -62,9 +62,11 @@ AO_B200_API int ao_lm_latent_prep(const void* proj, int dt, int64_t ld, int64_t 
  *   score_j = scale * (qa[h][t] . c_j + qr[t][h] . kr_j);  weights = softmax with exp(sink[h]) added to the denominator;
  *   out[t][h][:] = gate[t][h] * sum_j weight_j * c_j      (R numbers, in `dt`).
  * tile_first / tile_count [n_tiles]: runs of <= tile_tokens consecutive rows of ONE sequence (ao_lm_latent_attention_plan
- * gives tile_tokens).  n_split > 1 splits the keys over CTAs (max_pos + 1 keys are covered; workspace from
- * ao_lm_latent_attention_workspace_bytes). */
-AO_B200_API int ao_lm_latent_attention_plan(int H, int* tile_tokens);
+ * gives tile_tokens for a storage type and shape).  1 < n_split <= 64 splits the keys over CTAs (max_pos + 1 keys are
+ * covered; workspace from ao_lm_latent_attention_workspace_bytes).
+ * bf16 storage with R a multiple of 64 (<= 512) and dr a multiple of 16 runs on the tensor cores: queries and weights stay
+ * fp32, split into two TF32 parts each, against the cached rows (exact in TF32); every other case is fp32 FMA code. */
+AO_B200_API int ao_lm_latent_attention_plan(int dt, int H, int R, int dr, int* tile_tokens);
 AO_B200_API int64_t ao_lm_latent_attention_workspace_bytes(int64_t n, int H, int R, int n_split);
 AO_B200_API int ao_lm_latent_attention(const float* qa, const float* qr, const void* c_cache, const void* kr_cache, int dt,
                                        int64_t S, const int32_t* slot, const int32_t* pos, const int32_t* tile_first,

@@ -156,7 +156,7 @@ def _attention_case(H, R, dr, segs, S, dtype, n_split, far=None, seed=4):
     gate = torch.rand(n, H, generator=g)
     scale = 1.0 / math.sqrt(R + dr) * 2.0
     tt = ctypes.c_int()
-    lib.lm_check(L.ao_lm_latent_attention_plan(H, ctypes.byref(tt)), "plan")
+    lib.lm_check(L.ao_lm_latent_attention_plan(dt, H, R, dr, ctypes.byref(tt)), "plan")
     first, count = [], []
     at = 0
     for _, _, k in segs:
@@ -181,7 +181,7 @@ def _attention_case(H, R, dr, segs, S, dtype, n_split, far=None, seed=4):
     return out.double().cpu(), ref
 
 
-@pytest.mark.parametrize("H,R,dr", [(4, 64, 8), (3, 40, 6), (9, 33, 2), (2, 130, 16), (1, 16, 4)])
+@pytest.mark.parametrize("H,R,dr", [(4, 64, 8), (3, 40, 6), (9, 33, 2), (2, 130, 16), (1, 16, 4), (4, 64, 16), (3, 128, 32), (20, 192, 16), (16, 512, 64)])
 @pytest.mark.parametrize("n_split", [1, 3])
 def test_latent_attention_kernel_prompt_decode_and_mixed_rows(H, R, dr, n_split):
     # a prompt portion that starts in the middle of a key tile, a decoded token far in, the first tokens of a sequence
@@ -199,6 +199,8 @@ def test_latent_attention_kernel_finds_one_far_key(key):
         got, ref = _attention_case(2, 48, 4, [(0, 699, 1)], 704, torch.float32, n_split, far=(0, 1, key))
         assert torch.allclose(got, ref, rtol=2e-5, atol=2e-5)
         assert float(ref[0, 1].abs().max()) > 0.3          # the far key did dominate that head
+        got, ref = _attention_case(5, 64, 16, [(0, 699, 1)], 704, torch.bfloat16, n_split, far=(0, 3, key))   # tensor-core path
+        assert torch.allclose(got, ref, rtol=1e-2, atol=1e-2) and float(ref[0, 3].abs().max()) > 0.3
     # the same key seen from inside a prompt portion, just visible and not yet visible
     if key >= 2:
         got, ref = _attention_case(2, 48, 4, [(0, key - 2, 5)], 704, torch.float32, 1, far=(2, 0, key))
@@ -260,6 +262,9 @@ CONFIGS = {
     # sizes that other models make equal or one are all different / not one here; one expert of one, many heads
     "wide": dict(width=96, vocab=131, heads=9, dim=4, rot_dim=2, vdim=7, kv_rank=33, n_layers=2, share=(None, None),
                  experts=1, top=1, ff=17, shared_ff=9, mult=1.3, eps=1e-3, base=123.0),
+    # latent size a multiple of 64 and rotated size a multiple of 16: in bfloat16 the attention runs on the tensor cores
+    "tensor": dict(width=64, vocab=89, heads=5, dim=8, rot_dim=16, vdim=12, kv_rank=64, n_layers=3, share=(None, 0, None),
+                   experts=4, top=2, ff=16, shared_ff=16),
     "single": dict(width=32, vocab=50, heads=1, dim=16, rot_dim=8, vdim=32, kv_rank=16, n_layers=3, share=(None, 0, 0),
                    experts=7, top=7, ff=8, shared_ff=8),
 }
@@ -295,9 +300,10 @@ def test_layer_results_against_oracle_layer_by_layer():
         assert torch.allclose(x.double().cpu(), layers[upto - 1], rtol=1e-4, atol=1e-4), upto
 
 
+@pytest.mark.parametrize("name", ["mixed", "tensor"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_prefill_equals_token_by_token_and_portions(dtype):
-    cfg = O.random_config(**CONFIGS["mixed"])
+def test_prefill_equals_token_by_token_and_portions(dtype, name):
+    cfg = O.random_config(**CONFIGS[name])
     w = O.random_weights(cfg, seed=13)
     toks = _tokens(cfg, 70, 2)
     ref = O.forward(cfg, w, toks)
@@ -326,9 +332,10 @@ def test_long_piece_is_cut_inside_the_step(monkeypatch):
     assert _err(got, ref[[0, 15, 16, 17, 31, 32, 49]]) < F32_TOL
 
 
+@pytest.mark.parametrize("name", ["mixed", "tensor"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_batches_of_unequal_requests_equal_each_alone_and_slots_are_reused(dtype):
-    cfg = O.random_config(**CONFIGS["mixed"])
+def test_batches_of_unequal_requests_equal_each_alone_and_slots_are_reused(dtype, name):
+    cfg = O.random_config(**CONFIGS[name])
     w = O.random_weights(cfg, seed=15)
     reqs = {"a": _tokens(cfg, 37, 4), "b": _tokens(cfg, 5, 5), "c": _tokens(cfg, 21, 6), "d": _tokens(cfg, 30, 7)}
     ref = {k: O.forward(cfg, w, v) for k, v in reqs.items()}

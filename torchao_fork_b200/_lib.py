@@ -136,7 +136,7 @@ LM_SIGNATURES = {
     "ao_lm_scalar_norm_rows": [_vp, _vp, _i64, _i64, _vp, _i32, _f32, _vp, _vp],
     "ao_lm_latent_prep": [_vp, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _f32, _i32, _vp, _vp, _vp, _vp,
                           _vp, _i64, _vp, _vp, _vp, _vp],
-    "ao_lm_latent_attention_plan": [_i32, _p32],
+    "ao_lm_latent_attention_plan": [_i32, _i32, _i32, _i32, _p32],
     "ao_lm_latent_attention_workspace_bytes": [_i64, _i32, _i32, _i32],
     "ao_lm_latent_attention": [_vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32, _vp, _vp,
                                _i32, _i32, _vp, _i64, _vp, _vp],

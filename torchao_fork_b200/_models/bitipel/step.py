@@ -44,6 +44,14 @@ class StepEngine:
             torch.set_float32_matmul_precision("highest")
         self.sm_count = torch.cuda.get_device_properties(self.dev).multi_processor_count
         self.launches = 0
+        # rows of one sequence that an attention CTA shares its key tiles for, per attention shape of the model
+        import ctypes
+        self.tile_tokens = {}
+        for la in self.cfg.layers:
+            a = la.mixer
+            tt = ctypes.c_int()
+            _lib.lm_check(self.L.ao_lm_latent_attention_plan(self.dt, a.heads, a.kv_rank, a.rot_dim, ctypes.byref(tt)), "latent_attention_plan")
+            self.tile_tokens[(a.heads, a.kv_rank, a.rot_dim)] = tt.value
 
     # ------------------------------------------------------------------------------------------------ public
     @torch.no_grad()
@@ -102,24 +110,21 @@ class StepEngine:
         """One piece through all layers -> the stream that goes to the output norm, fp32 [n][W]."""
         n = len(tok)
         metas = {}
-        for H in {la.mixer.heads for la in self.cfg.layers}:
-            import ctypes
-            tt = ctypes.c_int()
-            _lib.lm_check(self.L.ao_lm_latent_attention_plan(H, ctypes.byref(tt)), "latent_attention_plan")
-            metas[H] = self._tiles(slot, pos, tt.value)
+        for key, tile_tokens in self.tile_tokens.items():
+            metas[key] = self._tiles(slot, pos, tile_tokens)
         # one host->device copy for all metadata
         parts = [tok.view(np.int32), slot, pos]
-        for H in sorted(metas):
-            parts += list(metas[H])
+        for key in sorted(metas):
+            parts += list(metas[key])
         packed = torch.from_numpy(np.concatenate(parts)).to(self.dev, non_blocking=True)
         o = 0
         d_tok = packed[o:o + 2 * n].view(torch.int64); o += 2 * n
         d_slot = packed[o:o + n]; o += n
         d_pos = packed[o:o + n]; o += n
         tiles = {}
-        for H in sorted(metas):
-            k = len(metas[H][0])
-            tiles[H] = (packed[o:o + k], packed[o + k:o + 2 * k], k)
+        for key in sorted(metas):
+            k = len(metas[key][0])
+            tiles[key] = (packed[o:o + k], packed[o + k:o + 2 * k], k)
             o += 2 * k
         return self._layers(n, d_tok, d_slot, d_pos, tiles, int(pos.max()), None, n <= MOE_GEMV_TOKENS)
 
@@ -130,7 +135,7 @@ class StepEngine:
         key_tiles = max_pos // 32 + 1
         if ctas >= self.sm_count or key_tiles <= 2:
             return 1
-        return max(1, min(key_tiles // 2, -(-2 * self.sm_count // ctas), 64))
+        return max(1, min(key_tiles, -(-2 * self.sm_count // ctas), 64))
 
     def _layers(self, n, d_tok, d_slot, d_pos, tiles, max_pos, n_split, gemv_experts) -> torch.Tensor:
         m, cfg, L, dt, dev = self.m, self.cfg, self.L, self.dt, self.dev
@@ -167,7 +172,7 @@ class StepEngine:
                 _p(cache.kr) if own else None, S, _p(qn), _p(qr), _p(gate), st), "latent_prep")
             # the key up-projection folded into the query: q_abs[h] = q_n[h] @ uk[h]  (fp32 result)
             qa = torch.bmm(qn, lay.uk, out_dtype=torch.float32) if tdt == torch.bfloat16 else torch.bmm(qn, lay.uk)
-            tf, tc, nt = tiles[H]
+            tf, tc, nt = tiles[(H, R, dr)]
             ns = n_split if n_split is not None else self._splits(nt, H, max_pos)
             ws_bytes = int(L.ao_lm_latent_attention_workspace_bytes(n, H, R, ns))
             ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
@@ -298,11 +303,10 @@ class GraphDecodeEngine:
         self.tile_first = torch.arange(B, dtype=torch.int32, device=dev)
         self.tile_count = torch.ones(B, dtype=torch.int32, device=dev)
         self.logits = torch.zeros(B, self.cfg.vocab_size, dtype=torch.float32, device=dev)
-        heads = {la.mixer.heads for la in self.cfg.layers}
-        self.tiles = {H: (self.tile_first, self.tile_count, B) for H in heads}
+        self.tiles = {key: (self.tile_first, self.tile_count, B) for key in self.eng.tile_tokens}
         # a fixed number of key splits over the whole cache: CTAs past a sequence's length leave at once
-        ctas = B * max(-(-((H + 3) // 4) // 8) for H in heads)
-        self.n_split = max(1, min(-(-self.S // 64), -(-2 * self.eng.sm_count // ctas), 64))
+        ctas = B * max(-(-H // 16) for H, _, _ in self.eng.tile_tokens)
+        self.n_split = max(1, min(-(-self.S // 32), -(-2 * self.eng.sm_count // ctas), 64))
         self.graph = None
         self.graph_stream = None
         self._noise = None
