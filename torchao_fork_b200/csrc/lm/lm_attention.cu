@@ -112,13 +112,35 @@ latent_attn_kernel(const float* __restrict__ qa, const float* __restrict__ qr, c
   // the warp's four query rows, interleaved so that one 16-byte broadcast load feeds four score rows
   float* myq = qs + (size_t)warp * D * 4;
   if (active) {
-    for (int d = lane; d < D; d += 32) {
+    const bool qvec = R % 4 == 0 && dr % 4 == 0 && reinterpret_cast<uintptr_t>(qa) % 16 == 0 && reinterpret_cast<uintptr_t>(qr) % 16 == 0;
+    if (qvec) {
+      // 16-byte loads, the four heads' chunks of one coordinate group in flight together
+      for (int ch = lane; ch < D / 4; ch += 32) {
+        const int d = ch * 4;
+        uint4 v[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int h = head0 + r;
-        float v = 0.f;
-        if (h < H) v = d < R ? qa[((int64_t)h * n + t) * R + d] : qr[(t * H + h) * dr + (d - R)];
-        myq[d * 4 + r] = v;
+        for (int r = 0; r < 4; ++r) {
+          const int h = head0 + r;
+          v[r] = make_uint4(0, 0, 0, 0);
+          if (h < H) v[r] = ld16(d < R ? qa + ((int64_t)h * n + t) * R + d : qr + (t * H + h) * dr + (d - R));
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          myq[(d + 0) * 4 + r] = __uint_as_float(v[r].x);
+          myq[(d + 1) * 4 + r] = __uint_as_float(v[r].y);
+          myq[(d + 2) * 4 + r] = __uint_as_float(v[r].z);
+          myq[(d + 3) * 4 + r] = __uint_as_float(v[r].w);
+        }
+      }
+    } else {
+      for (int d = lane; d < D; d += 32) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int h = head0 + r;
+          float v = 0.f;
+          if (h < H) v = d < R ? qa[((int64_t)h * n + t) * R + d] : qr[(t * H + h) * dr + (d - R)];
+          myq[d * 4 + r] = v;
+        }
       }
     }
   }
@@ -297,17 +319,39 @@ latent_attn_mma_kernel(const float* __restrict__ qa, const float* __restrict__ q
   const int cr = R / 8, cpk = cr + dr / 8, total_chunks = kKeys * cpk;
   uint4 pf[kPrefetch];
   fetch_tile<T>(pf, cbase, kbase, k_lo, k_hi, cpk, cr, R, dr, total_chunks);
-  // queries of the 16 rows, split into TF32 high and low parts
-  for (int i = threadIdx.x; i < kMmaRows * D; i += kWarps * 32) {
-    const int r = i / D, d = i - r * D, tq = r / HB, hh = r - tq * HB, h = head_base + hh;
-    float v = 0.f;
-    if (tq < count && h < H) {
-      const int64_t t = first + tq;
-      v = d < R ? qa[((int64_t)h * n + t) * R + d] : qr[(t * H + h) * dr + (d - R)];
+  // queries of the 16 rows, split into TF32 high and low parts; 16-byte loads, four in flight per thread
+  {
+    const int cq = D / 4, total_q = kMmaRows * cq;
+    for (int base = threadIdx.x; base < total_q; base += 4 * kWarps * 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int i = base + b * kWarps * 32;
+        v[b] = make_uint4(0, 0, 0, 0);
+        if (i < total_q) {
+          const int r = i / cq, d = (i - r * cq) * 4, tq = r / HB, hh = r - tq * HB, h = head_base + hh;
+          if (tq < count && h < H) {
+            const int64_t t = first + tq;
+            v[b] = ld16(d < R ? qa + ((int64_t)h * n + t) * R + d : qr + (t * H + h) * dr + (d - R));
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int i = base + b * kWarps * 32;
+        if (i < total_q) {
+          const int r = i / cq, d = (i - r * cq) * 4;
+          const uint32_t w[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x = __uint_as_float(w[e]);
+            const uint32_t hi = to_tf32(x);
+            qhi[r * DP + d + e] = __uint_as_float(hi);
+            qlo[r * DP + d + e] = __uint_as_float(to_tf32(x - __uint_as_float(hi)));
+          }
+        }
+      }
     }
-    const uint32_t hi = to_tf32(v);
-    qhi[r * DP + d] = __uint_as_float(hi);
-    qlo[r * DP + d] = __uint_as_float(to_tf32(v - __uint_as_float(hi)));
   }
   float o[NT][4];
 #pragma unroll
