@@ -129,12 +129,47 @@ def kernel_numbers(name, prompt_len, decode_ctx):
                                                    out.data_ptr(), st), "latent_attention")
         return timed(run, flush=flush)
 
-    # prompt attention: rows x visible keys x heads x (score: R + dr, weighted sum: R) multiply-adds
+    # prompt attention, expanded form: rows x visible keys x heads x (score: dn + dr, weighted sum: dv) multiply-adds are
+    # the algorithm; the kernel issues (dn + 2 dr) + 3 dv of them (fp32 rotated queries in two bf16 parts, fp32 weights
+    # in three).  The two GEMMs that up-project the cached latents into keys and values are timed beside it.
     n = prompt_len
+    dn, dv = a.dim, a.vdim
+    xt = ctypes.c_int()
+    L.ao_lm_latent_attention_expanded_plan(0, dn, dr, dv, ctypes.byref(xt))
+    if xt.value:
+        qn, qr = torch.randn(H, n, dn, **bf), torch.randn(n, H, dr, device=dev)
+        cl, kr = torch.randn(n, R, **bf), torch.randn(1, n, dr, **bf)
+        ukx, uvx = torch.randn(H * dn, R, **bf) / math.sqrt(R), torch.randn(R, H * dv, **bf) / math.sqrt(R)
+        kx, vx = torch.empty(n, H * dn, **bf), torch.empty(n, H * dv, **bf)
+        slot = torch.zeros(n, dtype=torch.int32, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        tfst = torch.arange(0, n, xt.value, dtype=torch.int32, device=dev)
+        tcnt, trow = torch.clamp(n - tfst, max=xt.value).int(), torch.zeros_like(tfst)
+        sink, gate = torch.zeros(H, **bf), torch.ones(n, H, device=dev)
+        out = torch.empty(n, H * dv, **bf)
+
+        def expand():
+            torch.mm(cl, ukx.t(), out=kx)
+            torch.mm(cl, uvx, out=vx)
+
+        def expanded():
+            _lib.lm_check(L.ao_lm_latent_attention_expanded(
+                qn.data_ptr(), qr.data_ptr(), kx.data_ptr(), vx.data_ptr(), kr.data_ptr(), 0, n, slot.data_ptr(), pos.data_ptr(),
+                tfst.data_ptr(), tcnt.data_ptr(), trow.data_ptr(), tfst.numel(), n, H, dn, dr, dv, a.scale, sink.data_ptr(),
+                gate.data_ptr(), out.data_ptr(), st), "latent_attention_expanded")
+        ms_x = timed(expand, flush=flush)
+        ms = timed(expanded, flush=flush)
+        pairs = n * (n + 1) / 2
+        flops, issued = 2.0 * pairs * H * (dn + dr + dv), 2.0 * pairs * H * (dn + 2 * dr + 3 * dv)
+        res["latent_attention_prefill"] = {
+            "tokens": n, "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 2), "frac_bf16_tensor_peak": round(flops / ms / 1e9 / tf, 4),
+            "issued_tflops": round(issued / ms / 1e9, 2), "frac_issued": round(issued / ms / 1e9 / tf, 4),
+            "expand_gemms_ms": round(ms_x, 3)}
+        del qn, qr, cl, kr, kx, vx, out
+    # the folded form (what decoded tokens use) on the same prompt, for the record: (R + dr) + R multiply-adds per pair
     ms = attention(n, 0, 1)
     flops = 2.0 * (n * (n + 1) / 2) * H * (2 * R + dr)
-    res["latent_attention_prefill"] = {"tokens": n, "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 2),
-                                       "frac_bf16_tensor_peak": round(flops / ms / 1e9 / tf, 4)}
+    res["latent_attention_folded_on_a_prompt"] = {"tokens": n, "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 2)}
     q = torch.randn(1, cfg.width // 128, n, 128, **bf)
     k = torch.randn(1, cfg.width // 128, n, 128, **bf)
     ms = timed(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, k, is_causal=True), flush=flush)
@@ -147,6 +182,24 @@ def kernel_numbers(name, prompt_len, decode_ctx):
     byts = (decode_ctx + 1) * (R + dr) * 2
     res["latent_attention_decode"] = {"context": decode_ctx, "splits": ns, "us": round(ms * 1e3, 2), "cache_bytes": byts,
                                       "gbs": round(byts / ms / 1e6, 1), "frac_hbm": round(byts / ms / 1e6 / hbm, 4)}
+    # the Llama family's decode attention at the same context: K and V rows of width / 512 heads of 128, read once
+    core = _lib.lib()
+    Hq, Hkv, S = W // 128, max(1, W // 512), decode_ctx + 1
+    q1 = torch.randn(1, Hq, 128, **bf)
+    kc, vc = torch.randn(1, Hkv, S, 128, **bf), torch.randn(1, Hkv, S, 128, **bf)
+    ipos = torch.full((1,), decode_ctx, dtype=torch.int32, device=dev)
+    o1 = torch.empty(1, Hq, 128, **bf)
+    lns = max(1, min(64, -(-S // 32)))
+    lws = torch.zeros(max(16, int(core.ao_b200_decode_attention_workspace_bytes(1, Hq, lns))), dtype=torch.uint8, device=dev)
+
+    def llama_decode_attention():
+        _lib.check(core.ao_b200_decode_attention(q1.data_ptr(), kc.data_ptr(), vc.data_ptr(), ipos.data_ptr(), o1.data_ptr(), 1, Hq,
+                                                 Hkv, 128, S, 1.0 / math.sqrt(128), lns, lws.data_ptr(), lws.numel(), st),
+                   "decode_attention")
+    ms = timed(llama_decode_attention, flush=flush)
+    byts = 2 * Hkv * S * 128 * 2
+    res["llama_attention_decode"] = {"context": decode_ctx, "splits": lns, "us": round(ms * 1e3, 2), "cache_bytes": byts,
+                                     "gbs": round(byts / ms / 1e6, 1), "frac_hbm": round(byts / ms / 1e6 / hbm, 4)}
     # experts of one decoded token: top x (gate, up, down) matrices + the shared expert, read once
     tdt = torch.bfloat16
     x = torch.randn(1, W, **bf)

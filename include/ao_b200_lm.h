@@ -74,6 +74,23 @@ AO_B200_API int ao_lm_latent_attention(const float* qa, const float* qr, const v
                                        const void* sink, const float* gate, int max_pos, int n_split, void* workspace,
                                        int64_t workspace_bytes, void* out, void* stream);
 
+/* The same attention for prompt portions, in the expanded form (bf16 storage; tensor cores): the caller has up-projected
+ * the cached latents of every sequence in the step into keys kx[row][h][dn] and values vx[row][h][dv], the rows of one
+ * sequence contiguous from key 0;
+ *   score_j = scale * (qn[h][t] . kx_j[h] + qr[t][h] . kr_j);  the same sink, gate and causal mask;  out[t][h][dv] in bf16.
+ * tile_first / tile_count [n_tiles]: runs of <= tile_tokens consecutive rows of ONE sequence at consecutive positions;
+ * tile_kv_row[tile]: the row of kx / vx that holds key 0 of the tile's sequence.  The plan call gives tile_tokens, or 0
+ * when the shape is not covered (dn, dr, dv multiples of 16, dv up to 128): use ao_lm_latent_attention then.
+ * Scores accumulate in fp32 (the fp32 rotated query part as two bf16 parts); the fp32 weights enter the value product
+ * as three bf16 parts, i.e. exactly. */
+AO_B200_API int ao_lm_latent_attention_expanded_plan(int dt, int dn, int dr, int dv, int* tile_tokens);
+AO_B200_API int ao_lm_latent_attention_expanded(const void* qn, const float* qr, const void* kx, const void* vx,
+                                                const void* kr_cache, int dt, int64_t S, const int32_t* slot,
+                                                const int32_t* pos, const int32_t* tile_first, const int32_t* tile_count,
+                                                const int32_t* tile_kv_row, int n_tiles, int64_t n, int H, int dn, int dr,
+                                                int dv, float scale, const void* sink, const float* gate, void* out,
+                                                void* stream);
+
 /* Router: scores = softmax over all E logits (fp32 accumulation of h . w_router[e]); the `top` largest (ties: lowest
  * index) -> idx[t][top], weight[t][top] = their scores, not renormalised. */
 AO_B200_API int ao_lm_router_topk(const void* h, const void* w_router, int dt, int64_t n, int64_t width, int E, int top,

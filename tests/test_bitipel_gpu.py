@@ -207,6 +207,81 @@ def test_latent_attention_kernel_finds_one_far_key(key):
         assert torch.allclose(got, ref, rtol=2e-5, atol=2e-5)
 
 
+def _expanded_case(H, dn, dr, dv, segs, S, far=None, seed=5):
+    """The prompt-portion kernel on random queries, per-head keys / values and cached rotated key parts.
+    segs: [(slot, first position, count)]; every sequence's keys 0 .. its last position lie one after the other."""
+    lib, L = _lm()
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    n_slots = max(s for s, _, _ in segs) + 1
+    slot = torch.cat([torch.full((k,), s) for s, _, k in segs]).int()
+    pos = torch.cat([torch.arange(p, p + k) for _, p, k in segs]).int()
+    n = len(slot)
+    qn = torch.randn(H, n, dn, generator=g).to(bf)
+    qr = torch.randn(n, H, dr, generator=g)
+    kr = torch.randn(n_slots, S, dr, generator=g).to(bf)
+    rows, row0 = 0, {}
+    for s, p, k in segs:
+        row0[s] = rows
+        rows += p + k
+    kx = torch.randn(rows, H, dn, generator=g).to(bf)
+    vx = torch.randn(rows, H, dv, generator=g).to(bf)
+    if far is not None:       # (row, head, key): that key is aligned with the row's query so that its score stands out
+        t, h, key = far
+        kx[row0[int(slot[t])] + key, h] = (qn[h, t].float() / qn[h, t].float().norm() * 8.0).to(bf)
+    sink = torch.randn(H, generator=g).to(bf)
+    gate = 0.5 + 0.5 * torch.rand(n, H, generator=g)
+    scale = 1.0 / math.sqrt(dn + dr) * 2.0
+    tt = ctypes.c_int()
+    lib.lm_check(L.ao_lm_latent_attention_expanded_plan(lib.DT_BF16, dn, dr, dv, ctypes.byref(tt)), "plan")
+    assert tt.value > 0
+    first, count, kvrow = [], [], []
+    at = 0
+    for s, _, k in segs:
+        for f in range(at, at + k, tt.value):
+            first.append(f)
+            count.append(min(tt.value, at + k - f))
+            kvrow.append(row0[s])
+        at += k
+    dev = lambda t: t.cuda()
+    tf, tc, tr = dev(torch.tensor(first).int()), dev(torch.tensor(count).int()), dev(torch.tensor(kvrow).int())
+    out = torch.full((n, H, dv), float("nan"), dtype=bf, device="cuda")
+    d = [dev(t) for t in (qn, qr, kx, vx, kr, slot, pos, sink, gate)]
+    lib.lm_check(L.ao_lm_latent_attention_expanded(
+        d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(), d[4].data_ptr(), lib.DT_BF16, S, d[5].data_ptr(),
+        d[6].data_ptr(), tf.data_ptr(), tc.data_ptr(), tr.data_ptr(), len(first), n, H, dn, dr, dv, scale, d[7].data_ptr(),
+        d[8].data_ptr(), out.data_ptr(), _st()), "latent_attention_expanded")
+    ref = torch.empty(n, H, dv, dtype=O.F64)
+    for t in range(n):
+        sl, last = int(slot[t]), int(pos[t]) + 1
+        k = kx[row0[sl]: row0[sl] + last].double()
+        sc = (torch.einsum("hd,shd->hs", qn[:, t].double(), k) + torch.einsum("hd,sd->hs", qr[t].double(), kr[sl, :last].double())) * scale
+        p = O.sink_softmax(sc, sink.double().view(H, 1))
+        ref[t] = torch.einsum("hs,shd->hd", p, vx[row0[sl]: row0[sl] + last].double()) * gate[t].double().view(H, 1)
+    return out.double().cpu(), ref
+
+
+@pytest.mark.parametrize("H,dn,dr,dv", [(3, 16, 16, 32), (2, 32, 0, 64), (5, 48, 32, 112), (1, 16, 32, 16), (4, 128, 64, 128)])
+def test_expanded_attention_kernel_portions_tiles_and_first_tokens(H, dn, dr, dv):
+    # a portion that starts inside a key tile and spans three row tiles, one row far in, the first tokens, a full tile
+    segs = [(0, 29, 140), (1, 150, 1), (2, 0, 3), (3, 64, 64)]
+    got, ref = _expanded_case(H, dn, dr, dv, segs, 176)
+    assert torch.allclose(got, ref, rtol=1e-2, atol=1e-2)
+    assert float((got - ref).abs().max()) < 1.2e-2 and float((got - ref).pow(2).mean().sqrt()) < 2e-3   # bf16 output rounding only
+
+
+@pytest.mark.parametrize("key", [0, 1, 62, 63, 64, 65, 127, 128, 300])
+def test_expanded_attention_kernel_finds_one_far_key_and_respects_the_mask(key):
+    """One key carries almost all the weight of one row: seen from rows before it (masked), at it and after it."""
+    for first in (max(0, key - 2), max(0, key - 63), max(0, key - 64)):
+        count = 70
+        t = key - first           # the row AT the key
+        for row in (t, min(count - 1, t + 1), count - 1):
+            got, ref = _expanded_case(2, 16, 16, 32, [(0, first, count)], first + count, far=(row, 1, key))
+            assert torch.allclose(got, ref, rtol=1e-2, atol=1e-2), (first, row)
+            assert float(ref[row, 1].abs().max()) > 0.2
+
+
 @pytest.mark.parametrize("E,top,W", [(5, 2, 70), (1, 1, 64), (40, 6, 96), (8, 8, 33)])
 def test_router_kernel_softmax_over_all_then_top(E, top, W):
     lib, L = _lm()
@@ -265,6 +340,10 @@ CONFIGS = {
     # latent size a multiple of 64 and rotated size a multiple of 16: in bfloat16 the attention runs on the tensor cores
     "tensor": dict(width=64, vocab=89, heads=5, dim=8, rot_dim=16, vdim=12, kv_rank=64, n_layers=3, share=(None, 0, None),
                    experts=4, top=2, ff=16, shared_ff=16),
+    # head sizes that the prompt-portion (expanded) attention kernel covers in bfloat16; latent size that keeps decoding
+    # on the fp32 path: a step of 32 or more tokens per sequence and a smaller one take different kernels
+    "expanded": dict(width=64, vocab=101, heads=3, dim=16, rot_dim=16, vdim=32, kv_rank=40, n_layers=3, share=(None, 0, None),
+                     experts=6, top=2, ff=24, shared_ff=16),
     "single": dict(width=32, vocab=50, heads=1, dim=16, rot_dim=8, vdim=32, kv_rank=16, n_layers=3, share=(None, 0, 0),
                    experts=7, top=7, ff=8, shared_ff=8),
 }
@@ -300,9 +379,13 @@ def test_layer_results_against_oracle_layer_by_layer():
         assert torch.allclose(x.double().cpu(), layers[upto - 1], rtol=1e-4, atol=1e-4), upto
 
 
-@pytest.mark.parametrize("name", ["mixed", "tensor"])
+@pytest.mark.parametrize("name", ["mixed", "tensor", "expanded"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_prefill_equals_token_by_token_and_portions(dtype, name):
+    _check_portions(dtype, name)
+
+
+def _check_portions(dtype, name):
     cfg = O.random_config(**CONFIGS[name])
     w = O.random_weights(cfg, seed=13)
     toks = _tokens(cfg, 70, 2)
@@ -332,9 +415,23 @@ def test_long_piece_is_cut_inside_the_step(monkeypatch):
     assert _err(got, ref[[0, 15, 16, 17, 31, 32, 49]]) < F32_TOL
 
 
-@pytest.mark.parametrize("name", ["mixed", "tensor"])
+@pytest.mark.parametrize("name", ["mixed", "tensor", "expanded"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_batches_of_unequal_requests_equal_each_alone_and_slots_are_reused(dtype, name):
+    _check_batches(dtype, name)
+
+
+def test_expanded_attention_for_every_portion_and_batch(monkeypatch):
+    """With the threshold taken down, portions of two tokens and every row of a mixed batch (a sequence that brings one
+    token beside longer ones, a reused slot) attend through the prompt-portion kernel."""
+    from torchao_fork_b200._models.bitipel import step as S
+    monkeypatch.setattr(S, "EXPAND_MIN_TOKENS", 2)
+    _check_portions(torch.bfloat16, "expanded")
+    monkeypatch.setattr(S, "EXPAND_MIN_TOKENS", 1)
+    _check_batches(torch.bfloat16, "expanded")
+
+
+def _check_batches(dtype, name):
     cfg = O.random_config(**CONFIGS[name])
     w = O.random_weights(cfg, seed=15)
     reqs = {"a": _tokens(cfg, 37, 4), "b": _tokens(cfg, 5, 5), "c": _tokens(cfg, 21, 6), "d": _tokens(cfg, 30, 7)}

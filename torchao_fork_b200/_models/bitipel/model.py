@@ -197,6 +197,9 @@ class Bitipel(nn.Module):
             L.w_in = buf(p + "mix.in", torch.cat(parts, 0))                      # [q | dkv | gate][W]: one GEMM
             L.uk = buf(p + "mix.uk", get(p + "mix.uk", (H * dn, R)).view(H, dn, R))   # q_abs[h] = q_n[h] @ uk[h]
             L.uvT = buf(p + "mix.uvT", get(p + "mix.uv", (H * dv, R)).view(H, dv, R).transpose(1, 2))   # [H][R][dv]
+            # the same two matrices as [R][H dn] / [R][H dv] operands: keys and values of a whole prompt in one GEMM each
+            L.ukx = L.uk.view(H * dn, R)
+            L.uvx = buf(p + "mix.uvx", get(p + "mix.uv", (H * dv, R)).t())
             L.sink = buf(p + "mix.sink", get(p + "mix.sink", (H,)))
             L.o = buf(p + "mix.o", get(p + "mix.o", (W, H * dv)))
             half = m.rot_dims // 2

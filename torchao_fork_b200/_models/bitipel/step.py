@@ -24,6 +24,11 @@ from .model import GLU_ALPHA, Bitipel
 MAX_STEP_TOKENS = 2048
 # up to this many tokens the experts run as index-driven matrix-vector kernels, beyond it as GEMMs over sorted rows
 MOE_GEMV_TOKENS = 16
+# prompt portions of at least this many tokens per sequence (on average over the step) attend in the expanded form:
+# the sequence's cached latents are up-projected into per-head keys and values once per layer and step
+EXPAND_MIN_TOKENS = 32
+# ... unless the expanded keys and values of all sequences of the step would take more than this
+EXPAND_MAX_BYTES = 4 << 30
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -52,6 +57,15 @@ class StepEngine:
             tt = ctypes.c_int()
             _lib.lm_check(self.L.ao_lm_latent_attention_plan(self.dt, a.heads, a.kv_rank, a.rot_dim, ctypes.byref(tt)), "latent_attention_plan")
             self.tile_tokens[(a.heads, a.kv_rank, a.rot_dim)] = tt.value
+        # attention shapes that the expanded (prompt) kernel covers, and its tile
+        self.expand_ok, self.expand_tile = {}, 0
+        for la in self.cfg.layers:
+            a = la.mixer
+            tt = ctypes.c_int()
+            _lib.lm_check(self.L.ao_lm_latent_attention_expanded_plan(self.dt, a.dim, a.rot_dim, a.vdim, ctypes.byref(tt)),
+                          "latent_attention_expanded_plan")
+            self.expand_ok[(a.dim, a.rot_dim, a.vdim)] = tt.value > 0
+            self.expand_tile = max(self.expand_tile, tt.value)
 
     # ------------------------------------------------------------------------------------------------ public
     @torch.no_grad()
@@ -112,10 +126,13 @@ class StepEngine:
         metas = {}
         for key, tile_tokens in self.tile_tokens.items():
             metas[key] = self._tiles(slot, pos, tile_tokens)
+        expand = self._expand_plan(slot, pos)
         # one host->device copy for all metadata
         parts = [tok.view(np.int32), slot, pos]
         for key in sorted(metas):
             parts += list(metas[key])
+        if expand is not None:
+            parts += list(expand[0])
         packed = torch.from_numpy(np.concatenate(parts)).to(self.dev, non_blocking=True)
         o = 0
         d_tok = packed[o:o + 2 * n].view(torch.int64); o += 2 * n
@@ -126,7 +143,39 @@ class StepEngine:
             k = len(metas[key][0])
             tiles[key] = (packed[o:o + k], packed[o + k:o + 2 * k], k)
             o += 2 * k
+        if expand is not None:
+            k = len(expand[0][0])
+            tiles["expanded"] = (packed[o:o + k], packed[o + k:o + 2 * k], packed[o + 2 * k:o + 3 * k], k, expand[1], expand[2])
         return self._layers(n, d_tok, d_slot, d_pos, tiles, int(pos.max()), None, n <= MOE_GEMV_TOKENS)
+
+    def _expand_plan(self, slot: np.ndarray, pos: np.ndarray):
+        """When the step's sequences bring enough tokens each: ((tile_first, tile_count, tile_kv_row), [(slot, keys, row)],
+        rows) — tiles of the expanded attention kernel, and where each sequence's keys 0 .. its last position go in the
+        step's expanded key / value buffers.  None: the folded (decode) form serves the step."""
+        if not self.expand_tile:
+            return None
+        n = len(slot)
+        brk = np.flatnonzero((slot[1:] != slot[:-1]) | (pos[1:] != pos[:-1] + 1)) + 1
+        starts, ends = np.concatenate([[0], brk]), np.concatenate([brk, [n]])
+        if n < EXPAND_MIN_TOKENS * len(starts):
+            return None
+        first, count, kvrow, hist, rows, seen = [], [], [], [], 0, {}
+        for s, e in zip(starts, ends):
+            sl, keys = int(slot[s]), int(pos[e - 1]) + 1
+            if sl in seen:          # a sequence in two runs of one step: not a case worth a second copy of its keys
+                return None
+            seen[sl] = rows
+            f = np.arange(s, e, self.expand_tile)
+            first.append(f)
+            count.append(np.minimum(self.expand_tile, e - f))
+            kvrow.append(np.full(len(f), rows))
+            hist.append((sl, keys, rows))
+            rows += keys
+        per_row = max(la.mixer.heads * (la.mixer.dim + la.mixer.vdim) for la in self.cfg.layers) * 2
+        if rows * per_row > EXPAND_MAX_BYTES:
+            return None
+        return ((np.concatenate(first).astype(np.int32), np.concatenate(count).astype(np.int32),
+                 np.concatenate(kvrow).astype(np.int32)), hist, rows)
 
     def _splits(self, n_tiles: int, H: int, max_pos: int) -> int:
         """Key splits of the attention launch: enough CTAs to fill the GPU when few tokens attend over many keys."""
@@ -170,20 +219,15 @@ class StepEngine:
                 _p(proj), dt, proj.shape[1], n, H, dn, dr, R, lay.q_off, lay.kv_off, lay.g_off, _p(lay.c_norm), cfg.norm_eps,
                 a.rot_dims, _p(lay.inv_freq), _p(d_slot), _p(d_pos), _p(cache.c) if own else None,
                 _p(cache.kr) if own else None, S, _p(qn), _p(qr), _p(gate), st), "latent_prep")
-            # the key up-projection folded into the query: q_abs[h] = q_n[h] @ uk[h]  (fp32 result)
-            qa = torch.bmm(qn, lay.uk, out_dtype=torch.float32) if tdt == torch.bfloat16 else torch.bmm(qn, lay.uk)
-            tf, tc, nt = tiles[(H, R, dr)]
-            ns = n_split if n_split is not None else self._splits(nt, H, max_pos)
-            ws_bytes = int(L.ao_lm_latent_attention_workspace_bytes(n, H, R, ns))
-            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-            olat = torch.empty(n, H, R, **act)
-            _lib.lm_check(L.ao_lm_latent_attention(
-                _p(qa), _p(qr), _p(cache.c), _p(cache.kr), dt, S, _p(d_slot), _p(d_pos), _p(tf), _p(tc), nt, n, H, R, dr,
-                a.scale, _p(lay.sink), _p(gate), max_pos, ns, _p(ws), ws.numel(), _p(olat), st), "latent_attention")
-            ov = torch.bmm(olat.transpose(0, 1), lay.uvT)                       # [H][n][dv]
-            y = torch.mm(ov.transpose(0, 1).reshape(n, H * dv), lay.o.t())      # [n][W]
+            xp = tiles.get("expanded") if self.expand_ok[(dn, dr, dv)] else None
+            if xp is not None:
+                y = self._attend_expanded(lay, a, cache, xp, qn, qr, gate, d_slot, d_pos, n, st)
+                launches += 2 + 2 * len(xp[4])
+            else:
+                y = self._attend_folded(lay, a, cache, tiles, qn, qr, gate, d_slot, d_pos, n, max_pos, n_split, st)
+                launches += 4 + (1 if self._last_splits > 1 else 0)
             nxt = avg[i & 1]
-            launches += 9 + (1 if ns > 1 else 0)
+            launches += 4   # token shift, input projection, split / cache append, residual add with norm
             if f is None:
                 _lib.lm_check(L.ao_lm_residual_norm(
                     _p(x), _p(y), dt, _p(lay.norm1), dt, cfg.residual_mult, cfg.norm_eps, n, W, _p(streams[i + 1]),
@@ -202,6 +246,44 @@ class StepEngine:
             x = nxt
         self.launches = launches
         return x
+
+    def _attend_folded(self, lay, a, cache, tiles, qn, qr, gate, d_slot, d_pos, n, max_pos, n_split, st) -> torch.Tensor:
+        """Attention over the cached latents themselves: the key up-projection is folded into the query and the value
+        up-projection follows the weighted sum of latents (what a decoded token costs least with) -> [n][W]."""
+        L, dt, dev, tdt = self.L, self.dt, self.dev, self.m.dtype
+        H, dr, dv, R = a.heads, a.rot_dim, a.vdim, a.kv_rank
+        S = cache.c.shape[1]
+        # q_abs[h] = q_n[h] @ uk[h]  (fp32 result)
+        qa = torch.bmm(qn, lay.uk, out_dtype=torch.float32) if tdt == torch.bfloat16 else torch.bmm(qn, lay.uk)
+        tf, tc, nt = tiles[(H, R, dr)]
+        ns = n_split if n_split is not None else self._splits(nt, H, max_pos)
+        self._last_splits = ns
+        ws_bytes = int(L.ao_lm_latent_attention_workspace_bytes(n, H, R, ns))
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        olat = torch.empty(n, H, R, dtype=tdt, device=dev)
+        _lib.lm_check(L.ao_lm_latent_attention(
+            _p(qa), _p(qr), _p(cache.c), _p(cache.kr), dt, S, _p(d_slot), _p(d_pos), _p(tf), _p(tc), nt, n, H, R, dr,
+            a.scale, _p(lay.sink), _p(gate), max_pos, ns, _p(ws), ws.numel(), _p(olat), st), "latent_attention")
+        ov = torch.bmm(olat.transpose(0, 1), lay.uvT)                          # [H][n][dv]
+        return torch.mm(ov.transpose(0, 1).reshape(n, H * dv), lay.o.t())      # [n][W]
+
+    def _attend_expanded(self, lay, a, cache, xp, qn, qr, gate, d_slot, d_pos, n, st) -> torch.Tensor:
+        """Attention of prompt portions over per-head keys and values: every sequence's cached latents 0 .. its last
+        position are up-projected by two GEMMs, then one kernel runs all (token tile, head) pairs -> [n][W]."""
+        L, dt, dev, tdt = self.L, self.dt, self.dev, self.m.dtype
+        H, dn, dr, dv = a.heads, a.dim, a.rot_dim, a.vdim
+        tf, tc, trow, nt, hist, rows = xp
+        kx = torch.empty(rows, H * dn, dtype=tdt, device=dev)
+        vx = torch.empty(rows, H * dv, dtype=tdt, device=dev)
+        for sl, keys, r0 in hist:
+            c = cache.c[sl, :keys]
+            torch.mm(c, lay.ukx.t(), out=kx[r0:r0 + keys])
+            torch.mm(c, lay.uvx, out=vx[r0:r0 + keys])
+        oh = torch.empty(n, H * dv, dtype=tdt, device=dev)
+        _lib.lm_check(L.ao_lm_latent_attention_expanded(
+            _p(qn), _p(qr), _p(kx), _p(vx), _p(cache.kr), dt, cache.c.shape[1], _p(d_slot), _p(d_pos), _p(tf), _p(tc), _p(trow),
+            nt, n, H, dn, dr, dv, a.scale, _p(lay.sink), _p(gate), _p(oh), st), "latent_attention_expanded")
+        return torch.mm(oh, lay.o.t())
 
     def _experts(self, lay, f, xc, ffo, n, gemv, st) -> int:
         """ffo (fp32 [n][W]) = shared expert + sum of the chosen experts weighted by their router scores."""
@@ -239,10 +321,23 @@ class StepEngine:
         # rows sorted by expert: one GEMM pair per expert that has rows (the counts come back to the host)
         flat = ridx.view(-1)
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=f.experts).tolist()
+        counts = torch.bincount(flat, minlength=f.experts)
         mrows = n * f.top
+        grouped = tdt == torch.bfloat16 and W % 8 == 0 and f.ff % 8 == 0 and hasattr(torch, "_grouped_mm")
+        if grouped:
+            offs = torch.cumsum(counts, 0).to(torch.int32)
+        else:
+            counts = counts.tolist()   # fp32: one exact library GEMM pair per expert that has rows
         xs = torch.empty(mrows, W, dtype=tdt, device=dev)
         _lib.lm_check(L.ao_lm_gather_rows(_p(xc), dt, _p(order), f.top, mrows, W, _p(xs), st), "gather_rows")
+        if grouped:
+            # one grouped GEMM per projection over the sorted rows: the group ends stay on the device
+            gu = torch._grouped_mm(xs, lay.wgu.transpose(1, 2), offs=offs)
+            ya = torch.empty(mrows, f.ff, dtype=tdt, device=dev)
+            _lib.lm_check(L.ao_lm_glu_act(_p(gu), dt, mrows, f.ff, f.limit, GLU_ALPHA, _p(ya), st), "glu_act")
+            ys = torch._grouped_mm(ya, lay.wd.transpose(1, 2), offs=offs)
+            _lib.lm_check(L.ao_lm_scatter_add_rows(_p(ys), dt, _p(order), _p(rwt), f.top, mrows, W, _p(ffo), st), "scatter_add_rows")
+            return launches + 9
         ys = torch.empty(mrows, W, dtype=tdt, device=dev)
         ya = torch.empty(max(counts), f.ff, dtype=tdt, device=dev)
         at = 0
