@@ -85,6 +85,29 @@ def test_attention_tiles_follow_sequences():
     assert first.tolist() == [0] and count.tolist() == [1]
 
 
+def test_expanded_attention_plan_tiles_key_rows_and_threshold():
+    """Which steps attend in the expanded form, and where each sequence's keys go in the step's key / value buffers."""
+    from types import SimpleNamespace
+    from torchao_fork_b200._models.bitipel import step as S
+    from torchao_fork_b200._models.bitipel.step import StepEngine
+    cfg = bitipel_configs["Bitipel-test"]()
+    eng = SimpleNamespace(expand_tile=4, cfg=cfg)
+    # two sequences: 40 tokens from position 10, 35 tokens from position 0
+    slot = np.concatenate([np.full(40, 3), np.full(35, 1)]).astype(np.int32)
+    pos = np.concatenate([np.arange(10, 50), np.arange(35)]).astype(np.int32)
+    (first, count, row), hist, rows = StepEngine._expand_plan(eng, slot, pos)
+    assert hist == [(3, 50, 0), (1, 35, 50)] and rows == 85          # keys 0 .. last position of each, one after the other
+    assert first.tolist() == list(range(0, 40, 4)) + list(range(40, 75, 4))
+    assert count.tolist() == [4] * 10 + [4] * 8 + [3]
+    assert row.tolist() == [0] * 10 + [50] * 9
+    # fewer tokens per sequence than the threshold: the folded form serves the step
+    assert StepEngine._expand_plan(eng, slot[:S.EXPAND_MIN_TOKENS - 1], pos[:S.EXPAND_MIN_TOKENS - 1]) is None
+    one_each = np.arange(40, dtype=np.int32)
+    assert StepEngine._expand_plan(eng, one_each, np.zeros(40, np.int32)) is None
+    # no shape of the model is covered by the kernel
+    assert StepEngine._expand_plan(SimpleNamespace(expand_tile=0, cfg=cfg), slot, pos) is None
+
+
 def test_oracle_whole_sequence_equals_incremental_restatement():
     """The oracle's forward sees the whole sequence; restating one layer position by position with explicit carried
     state (previous input row, cached latents) must give the same numbers — the two readings of the equations agree."""

@@ -504,7 +504,9 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part_o, const
     (void)red;
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+  // blockIdx.y: which 128 output coordinates (one per thread), so that a decoded token's few rows still fill many SMs
+  const int d = blockIdx.y * blockDim.x + threadIdx.x;
+  if (d < R) {
     float acc = 0.f;
 #pragma unroll 8
     for (int s = 0; s < ns; ++s) acc = fmaf(part_o[(row * n_split + s) * R + d], wsplit[s], acc);
@@ -537,7 +539,7 @@ int launch(const float* qa, const float* qr, const void* c_cache, const void* kr
                                         tile_first, tile_count, n, H, R, dr, scale, HQ, tps, n_split,
                                         static_cast<const T*>(sink), gate, static_cast<T*>(out), part_o, part_ml);
   if (n_split > 1)
-    latent_attn_merge_kernel<T><<<(unsigned)(n * H), 128, 0, st>>>(part_o, part_ml, pos, H, R, tps, n_split,
+    latent_attn_merge_kernel<T><<<dim3((unsigned)(n * H), (unsigned)((R + 127) / 128)), 128, 0, st>>>(part_o, part_ml, pos, H, R, tps, n_split,
                                                                   static_cast<const T*>(sink), gate, static_cast<T*>(out));
   return lm_launch_status();
 }
@@ -568,7 +570,7 @@ int launch_mma(const float* qa, const float* qr, const void* c_cache, const void
                                         tile_first, tile_count, n, H, dr, scale, HB, tps, n_split, static_cast<const T*>(sink),
                                         gate, static_cast<T*>(out), part_o, part_ml);
   if (n_split > 1)
-    latent_attn_merge_kernel<T><<<(unsigned)(n * H), 128, 0, st>>>(part_o, part_ml, pos, H, R, tps, n_split,
+    latent_attn_merge_kernel<T><<<dim3((unsigned)(n * H), (unsigned)((R + 127) / 128)), 128, 0, st>>>(part_o, part_ml, pos, H, R, tps, n_split,
                                                                   static_cast<const T*>(sink), gate, static_cast<T*>(out));
   return lm_launch_status();
 }

@@ -224,13 +224,20 @@ latent_attn_expanded_kernel(const __nv_bfloat16* __restrict__ qn, const float* _
 #pragma unroll
       for (int j = 0; j < kPN / 16; ++j) {
 #pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          uint32_t b[4];
-          ldsm_x4_trans(b, vb_ptr + (size_t)j * 16 * VP + v * 16);
+        for (int v0 = 0; v0 < NV; v0 += 4) {   // four fragments at a time: eight accumulators between two uses of one
+          uint32_t b[4][4];
+#pragma unroll
+          for (int vv = 0; vv < 4; ++vv)
+            if (v0 + vv < NV) ldsm_x4_trans(b[vv], vb_ptr + (size_t)j * 16 * VP + (v0 + vv) * 16);
 #pragma unroll
           for (int part = 0; part < 3; ++part) {
-            mma_bf16(o[2 * v], pa[part][j], b[0], b[1]);
-            mma_bf16(o[2 * v + 1], pa[part][j], b[2], b[3]);
+#pragma unroll
+            for (int vv = 0; vv < 4; ++vv) {
+              if (v0 + vv < NV) {
+                mma_bf16(o[2 * (v0 + vv)], pa[part][j], b[vv][0], b[vv][1]);
+                mma_bf16(o[2 * (v0 + vv) + 1], pa[part][j], b[vv][2], b[vv][3]);
+              }
+            }
           }
         }
       }

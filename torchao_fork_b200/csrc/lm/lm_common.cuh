@@ -69,8 +69,8 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* w, const float* x
   float acc = 0.f;
   if (vec) {
     const uint4* w4 = reinterpret_cast<const uint4*>(w);
-    for (int64_t i = lane; i < K / 8; i += 32) {
-      const uint4 v = __ldg(w4 + i);
+    const int64_t nv = K / 8;
+    auto use = [&](const uint4& v, int64_t i) {
       const uint32_t r[4] = {v.x, v.y, v.z, v.w};
       const float* x = xs + i * 8;
 #pragma unroll
@@ -78,7 +78,16 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* w, const float* x
         acc = fmaf(__uint_as_float(r[j] << 16), x[2 * j], acc);
         acc = fmaf(__uint_as_float(r[j] & 0xFFFF0000u), x[2 * j + 1], acc);
       }
+    };
+    int64_t i = lane;
+    for (; i + 96 < nv; i += 128) {   // four 16-byte loads of the row in flight per lane before the first is used
+      const uint4 v0 = __ldg(w4 + i), v1 = __ldg(w4 + i + 32), v2 = __ldg(w4 + i + 64), v3 = __ldg(w4 + i + 96);
+      use(v0, i);
+      use(v1, i + 32);
+      use(v2, i + 64);
+      use(v3, i + 96);
     }
+    for (; i < nv; i += 32) use(__ldg(w4 + i), i);
   } else {
     for (int64_t i = lane; i < K; i += 32) acc = fmaf(__bfloat162float(w[i]), xs[i], acc);
   }
@@ -101,6 +110,83 @@ __device__ __forceinline__ float warp_dot(const float* w, const float* xs, int64
   }
   return warp_sum(acc);
 }
+// NR dot products of one warp at once: out[r] = sum_k rows[r][k] * xs[r][k] for r < nr (<= NR), bf16 rows of K elements
+// (K a multiple of 8, rows 16-byte aligned).  The loads of all rows, U vectors each, are issued before any is used: a
+// matrix-vector kernel is a chain of DRAM round trips per warp, and this makes the chain NR * U times shorter.
+template <int NR, int U>
+__device__ __forceinline__ void warp_dot_rows(const __nv_bfloat16* const (&rows)[NR], const float* const (&xs)[NR], int nr,
+                                              int64_t K, int lane, float (&out)[NR]) {
+  const int64_t nv = K / 8;
+  float acc[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+  for (int64_t i0 = lane; i0 < nv; i0 += 32 * U) {
+    uint4 v[NR][U];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + 32 * u;
+        v[r][u] = make_uint4(0, 0, 0, 0);
+        if (r < nr && i < nv) v[r][u] = __ldg(reinterpret_cast<const uint4*>(rows[r]) + i);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + 32 * u;
+        if (r < nr && i < nv) {
+          const uint32_t w[4] = {v[r][u].x, v[r][u].y, v[r][u].z, v[r][u].w};
+          const float* x = xs[r] + i * 8;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[r] = fmaf(__uint_as_float(w[j] << 16), x[2 * j], acc[r]);
+            acc[r] = fmaf(__uint_as_float(w[j] & 0xFFFF0000u), x[2 * j + 1], acc[r]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) out[r] = warp_sum(acc[r]);
+}
+
+// 16 bytes of storage type -> fp32
+__device__ __forceinline__ void unpack16(const uint4& u, float* dst, const __nv_bfloat16*) {
+  const uint32_t r[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    dst[2 * i] = __uint_as_float(r[i] << 16);
+    dst[2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void unpack16(const uint4& u, float* dst, const float*) {
+  dst[0] = __uint_as_float(u.x), dst[1] = __uint_as_float(u.y), dst[2] = __uint_as_float(u.z), dst[3] = __uint_as_float(u.w);
+}
+// dst[0..count) (fp32, shared memory) = src[0..count) by the whole block: 16-byte loads, four in flight per thread, when
+// the source is aligned; a matrix-vector kernel's activation row must not arrive one dependent load at a time
+template <typename T>
+__device__ __forceinline__ void stage_f32(const T* __restrict__ src, float* dst, int64_t count) {
+  constexpr int kPer = 16 / (int)sizeof(T);
+  int64_t done = 0;
+  if (reinterpret_cast<uintptr_t>(src) % 16 == 0) {
+    const int64_t nv = count / kPer, step = blockDim.x;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    int64_t i = threadIdx.x;
+    for (; i + 3 * step < nv; i += 4 * step) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __ldg(s4 + i + j * step);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) unpack16(v[j], dst + (i + j * step) * kPer, src);
+    }
+    for (; i < nv; i += step) unpack16(__ldg(s4 + i), dst + i * kPer, src);
+    done = nv * kPer;
+  }
+  for (int64_t i = done + threadIdx.x; i < count; i += blockDim.x) dst[i] = ldf(src + i);
+}
+
 template <typename T>
 __host__ __device__ __forceinline__ bool rows_vectorizable(const void* base, int64_t K) {
   return (K % (16 / (int)sizeof(T)) == 0) && (reinterpret_cast<uintptr_t>(base) % 16 == 0);

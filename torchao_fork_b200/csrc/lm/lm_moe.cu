@@ -4,27 +4,50 @@
 // the gather / scatter kernels at the end of this file around library GEMMs.
 #include "lm_common.cuh"
 
+#include <type_traits>
+
 using namespace lm;
 
 namespace {
 
 constexpr int kWarps = 8;
 
-// one CTA per token: E dot products (a warp each, round robin), then warp 0 does softmax + top-k
+// one CTA per token: E dot products (a warp each, round robin), then warp 0 does softmax + top-k.  A step of few tokens
+// has few CTAs: each then runs 32 warps, so that one token's router matrix is read by more loads in flight.
 template <typename T>
-__global__ void router_topk_kernel(const T* __restrict__ h, const T* __restrict__ wr, int64_t W, int E, int top,
+__global__ void __launch_bounds__(1024) router_topk_kernel(const T* __restrict__ h, const T* __restrict__ wr, int64_t W, int E, int top,
                                    int32_t* __restrict__ idx, float* __restrict__ weight) {
   extern __shared__ float sm[];
   float* xs = sm;          // [W]
   float* z = sm + W;       // [E]
   const int64_t t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) xs[w] = ldf(h + t * W + w);
+  stage_f32(h + t * W, xs, W);
   __syncthreads();
   const bool vec = rows_vectorizable<T>(wr, W);
-  for (int e = warp; e < E; e += kWarps) {
-    const float v = warp_dot(wr + (int64_t)e * W, xs, W, lane, vec);
-    if (lane == 0) z[e] = v;
+  const int nw = (int)(blockDim.x >> 5);
+  bool done = false;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    if (vec) {   // a warp's experts two at a time
+      for (int e = warp; e < E; e += 2 * nw) {
+        const int e2 = e + nw < E ? e + nw : e;
+        const T* const rows[2] = {wr + (int64_t)e * W, wr + (int64_t)e2 * W};
+        const float* const xr[2] = {xs, xs};
+        float v[2];
+        warp_dot_rows<2, 4>(rows, xr, e + nw < E ? 2 : 1, W, lane, v);
+        if (lane == 0) {
+          z[e] = v[0];
+          if (e + nw < E) z[e2] = v[1];
+        }
+      }
+      done = true;
+    }
+  }
+  if (!done) {
+    for (int e = warp; e < E; e += nw) {
+      const float v = warp_dot(wr + (int64_t)e * W, xs, W, lane, vec);
+      if (lane == 0) z[e] = v;
+    }
   }
   __syncthreads();
   if (warp != 0) return;
@@ -62,14 +85,28 @@ __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restri
   extern __shared__ float xs[];   // [W]
   const int64_t p = blockIdx.y, t = p / top;
   const int64_t e = idx ? idx[p] : 0;
-  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) xs[w] = ldf(h + t * W + w);
+  stage_f32(h + t * W, xs, W);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t f = (int64_t)blockIdx.x * kWarps + warp;
   if (f >= ff) return;
   const bool vec = rows_vectorizable<T>(wg, W) && rows_vectorizable<T>(wu, W);
-  const float a = warp_dot(wg + e * expert_stride + f * W, xs, W, lane, vec);
-  const float b = warp_dot(wu + e * expert_stride + f * W, xs, W, lane, vec);
+  float a, b;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    if (vec) {   // both rows together, four vectors each in flight
+      const T* const rows[2] = {wg + e * expert_stride + f * W, wu + e * expert_stride + f * W};
+      const float* const xr[2] = {xs, xs};
+      float ab[2];
+      warp_dot_rows<2, 4>(rows, xr, 2, W, lane, ab);
+      a = ab[0], b = ab[1];
+    } else {
+      a = warp_dot(wg + e * expert_stride + f * W, xs, W, lane, false);
+      b = warp_dot(wu + e * expert_stride + f * W, xs, W, lane, false);
+    }
+  } else {
+    a = warp_dot(wg + e * expert_stride + f * W, xs, W, lane, vec);
+    b = warp_dot(wu + e * expert_stride + f * W, xs, W, lane, vec);
+  }
   if (lane == 0) {
     // the projections' outputs are activations of the storage type: round them as a GEMM would
     T ra, rb;
@@ -88,13 +125,43 @@ __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict_
                                    float* __restrict__ out) {
   extern __shared__ float ys[];   // [top][ff]
   const int64_t t = blockIdx.y;
-  for (int64_t i = threadIdx.x; i < top * ff; i += blockDim.x) ys[i] = ldf(y + t * top * ff + i);
+  stage_f32(y + t * top * ff, ys, (int64_t)top * ff);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * kWarps + warp;
   if (w >= W) return;
   const bool vec = rows_vectorizable<T>(wd, ff);
   float acc = 0.f;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    if (vec) {   // the rows of up to four of the token's experts together, two vectors each in flight
+      for (int k0 = 0; k0 < top; k0 += 4) {
+        const int kn = min(4, top - k0);
+        const T* rows[4];
+        const float* yr[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k = k0 + (j < kn ? j : 0);
+          const int64_t e = idx ? idx[t * top + k] : 0;
+          rows[j] = wd + (e * W + w) * ff;
+          yr[j] = ys + (int64_t)k * ff;
+        }
+        const T* const rc[4] = {rows[0], rows[1], rows[2], rows[3]};
+        const float* const yc[4] = {yr[0], yr[1], yr[2], yr[3]};
+        float d[4];
+        warp_dot_rows<4, 2>(rc, yc, kn, ff, lane, d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < kn) {
+            T rd;
+            stf(&rd, d[j]);       // an expert's output is an activation of the storage type
+            acc = fmaf(weight ? weight[t * top + k0 + j] : 1.f, ldf(&rd), acc);
+          }
+        }
+      }
+      if (lane == 0) out[t * W + w] = (accumulate ? out[t * W + w] : 0.f) + acc;
+      return;
+    }
+  }
   for (int k = 0; k < top; ++k) {
     const int64_t e = idx ? idx[t * top + k] : 0;
     const float d = warp_dot(wd + (e * W + w) * ff, ys + (int64_t)k * ff, ff, lane, vec);
@@ -129,7 +196,7 @@ extern "C" int ao_lm_router_topk(const void* h, const void* w_router, int dt, in
   LM_DISPATCH(dt, {
     auto kern = router_topk_kernel<T>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    kern<<<(unsigned)n, kWarps * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_router), width,
+    kern<<<(unsigned)n, (n <= 64 ? 32 : kWarps) * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_router), width,
                                                                E, top, idx, weight);
   });
   return lm_launch_status();

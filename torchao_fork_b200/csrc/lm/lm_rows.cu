@@ -8,6 +8,13 @@ using namespace lm;
 namespace {
 
 constexpr int kRowThreads = 256;
+// threads of a row's CTA: a step of few rows has few CTAs, so each row is spread over more threads (more loads in flight)
+inline unsigned row_threads(int64_t rows, int64_t width) {
+  if (rows >= 128) return kRowThreads;
+  unsigned t = kRowThreads;
+  while (t < 1024 && (int64_t)t * 4 < width) t *= 2;
+  return t;
+}
 
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int64_t* __restrict__ tok, int64_t W, float* __restrict__ x) {
@@ -153,9 +160,18 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int6
   const float* row = logits + blockIdx.x * ld;
   float best = -INFINITY;
   int64_t at = V;
-  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
+  int64_t i = threadIdx.x;
+  for (; i + 3 * (int64_t)blockDim.x < V; i += 4 * (int64_t)blockDim.x) {   // four loads in flight per thread
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = row[i + j * (int64_t)blockDim.x];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (v[j] > best) best = v[j], at = i + j * (int64_t)blockDim.x;     // ascending indices: the first of equals stays
+  }
+  for (; i < V; i += blockDim.x) {
     const float v = row[i];
-    if (v > best || (v == best && i < at)) best = v, at = i;
+    if (v > best) best = v, at = i;
   }
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -177,14 +193,14 @@ extern "C" int ao_lm_abi_version(void) { return 1; }
 
 extern "C" int ao_lm_embed(const void* table, int dt, const int64_t* tok, int64_t n, int64_t width, float* x, void* stream) {
   LM_CHECK_ARG(table && tok && x && n > 0 && width > 0);
-  LM_DISPATCH(dt, embed_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(static_cast<const T*>(table), tok, width, x));
+  LM_DISPATCH(dt, embed_kernel<T><<<(unsigned)n, row_threads(n, width), 0, lm_stream(stream)>>>(static_cast<const T*>(table), tok, width, x));
   return lm_launch_status();
 }
 
 extern "C" int ao_lm_token_shift(const float* x, const void* mu, int dt, const float* state, const int32_t* slot,
                                  const int32_t* pos, int64_t n, int64_t width, void* h, void* stream) {
   LM_CHECK_ARG(x && mu && state && slot && pos && h && n > 0 && width > 0);
-  LM_DISPATCH(dt, token_shift_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+  LM_DISPATCH(dt, token_shift_kernel<T><<<(unsigned)n, row_threads(n, width), 0, lm_stream(stream)>>>(
                       x, static_cast<const T*>(mu), state, slot, pos, width, static_cast<T*>(h)));
   return lm_launch_status();
 }
@@ -197,11 +213,11 @@ extern "C" int ao_lm_residual_norm(const float* x_in, const void* y, int y_dt, c
   LM_CHECK_ARG((!state || slot) && (!streams || (coef && avg_out && n_streams >= 0)));
   LM_DISPATCH(dt, {
     if (y_dt == AO_LM_F32)
-      residual_norm_kernel<T, float><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+      residual_norm_kernel<T, float><<<(unsigned)n, row_threads(n, width), 0, lm_stream(stream)>>>(
           x_in, static_cast<const float*>(y), static_cast<const T*>(g), mult, eps, n, width, x_out, state, slot, streams,
           n_streams, stream_stride, static_cast<const T*>(coef), avg_out, static_cast<T*>(cast_out));
     else if (y_dt == dt)
-      residual_norm_kernel<T, T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+      residual_norm_kernel<T, T><<<(unsigned)n, row_threads(n, width), 0, lm_stream(stream)>>>(
           x_in, static_cast<const T*>(y), static_cast<const T*>(g), mult, eps, n, width, x_out, state, slot, streams,
           n_streams, stream_stride, static_cast<const T*>(coef), avg_out, static_cast<T*>(cast_out));
     else
@@ -213,7 +229,7 @@ extern "C" int ao_lm_residual_norm(const float* x_in, const void* y, int y_dt, c
 extern "C" int ao_lm_scalar_norm_rows(const float* x, const int32_t* rows, int64_t m, int64_t width, const void* g, int dt,
                                       float eps, void* out, void* stream) {
   LM_CHECK_ARG(x && g && out && m > 0 && width > 0);
-  LM_DISPATCH(dt, scalar_norm_rows_kernel<T><<<(unsigned)m, kRowThreads, 0, lm_stream(stream)>>>(
+  LM_DISPATCH(dt, scalar_norm_rows_kernel<T><<<(unsigned)m, row_threads(m, width), 0, lm_stream(stream)>>>(
                       x, rows, width, static_cast<const T*>(g), eps, static_cast<T*>(out)));
   return lm_launch_status();
 }
@@ -225,7 +241,7 @@ extern "C" int ao_lm_latent_prep(const void* proj, int dt, int64_t ld, int64_t n
   LM_CHECK_ARG(proj && slot && pos && qn && qr && gate && n > 0 && H > 0 && dn >= 0 && dr >= 0 && R > 0);
   LM_CHECK_ARG(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || inv_freq));
   LM_CHECK_ARG(kv_off < 0 || (c_norm && c_cache && kr_cache && S > 0));
-  LM_DISPATCH(dt, latent_prep_kernel<T><<<(unsigned)n, kRowThreads, 0, lm_stream(stream)>>>(
+  LM_DISPATCH(dt, latent_prep_kernel<T><<<(unsigned)n, row_threads(n, (int64_t)H * (dn + dr)), 0, lm_stream(stream)>>>(
                       static_cast<const T*>(proj), ld, n, H, dn, dr, R, q_off, kv_off, g_off, static_cast<const T*>(c_norm), eps,
                       rot_dims, inv_freq, slot, pos, static_cast<T*>(c_cache), static_cast<T*>(kr_cache), S,
                       static_cast<T*>(qn), qr, gate));
@@ -249,6 +265,6 @@ extern "C" int ao_lm_add_cast(const void* b, int dt, int64_t count, float* a_ino
 
 extern "C" int ao_lm_argmax(const float* logits, int64_t ld, int64_t B, int64_t V, int64_t* out, void* stream) {
   LM_CHECK_ARG(logits && out && B > 0 && V > 0 && ld >= V);
-  argmax_kernel<<<(unsigned)B, 256, 0, lm_stream(stream)>>>(logits, ld, V, out);
+  argmax_kernel<<<(unsigned)B, 1024, 0, lm_stream(stream)>>>(logits, ld, V, out);
   return lm_launch_status();
 }
