@@ -1,4 +1,4 @@
-"""The boundary proved on the real reference package ("next" item 4; INTEGRATION.md sections 1 and 3):
+"""The boundary proved on the real reference package:
 tests/ref_binding_worker.py imports the unmodified reference from oracle/_ref, binds libao_b200.so into it exactly as
 INTEGRATION.md prescribes and runs the reference's own checks (test/test_ops.py:282-496 restated: the reference's test
 tree does not travel to the GPU box) — unpack bit-exact, dequant identical to the aten identity-matmul, opcheck with all

@@ -1,4 +1,4 @@
-"""CUDA-path parity pinned to the reference ITSELF running on the device ("next" items 2 and 4): the
+"""CUDA-path parity pinned to the reference ITSELF running on the device: the
 unmodified reference package (oracle/_ref) quantizes the same weights with `quantize_(lin.cuda(), ...)` in a subprocess
 (tests/ref_worker.py); this repo's CUDA path must reproduce its integers, scales and zeros BIT-EXACTLY and its linear
 outputs within the stated tolerance (SQNR >= 40 dB and mean-abs-rel < 1e-2 — the figure test_ops.py:113-117 uses for

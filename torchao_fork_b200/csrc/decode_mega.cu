@@ -1,7 +1,7 @@
 // One decode step of the gpt-fast Llama (torchao/_models/llama/model.py:342-486, generate.py:111-117) as ONE persistent,
 // cooperative launch: every SM runs one CTA for the whole token, and the weight stream never drains between projections.
 //
-// Why: with one launch per projection (round 1: 161 launches per token) each launch pays a fixed 3.5 - 5 us (dependency
+// Why: with one launch per projection (161 launches per token) each launch pays a fixed 3.5 - 5 us (dependency
 // resolution, cold instruction cache, activation staging, pipeline fill, drain) around 1.3 - 9.6 us of streaming; the step
 // ran at 0.43 of the HBM roofline.  Here a CTA is
 //   * 1 producer warp that walks the CTA's share of EVERY byte the token streams, in order — the int4 weights of every
