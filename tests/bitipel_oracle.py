@@ -36,10 +36,6 @@ def vector_norm(x, w, eps):
     return unit_rms(x, eps) * w
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def token_shift(h, mu, before):
     """h [T][W]: row t becomes h_t + (h_{t-1} - h_t) * mu with the UNSHIFTED h_{t-1}; `before` is the row that
     precedes row 0 (zeros at the start of a sequence)."""
