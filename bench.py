@@ -54,7 +54,7 @@ PROMPT_LEN = 8  # reference default prompt "Hello, my name is" ~ 6-8 tokens (gen
 
 
 def int4_gemv_bytes(m, n, k, g):
-    """algorithmic bytes of one int4 weight-only GEMM launch (SURVEY.md §8(d))"""
+    """algorithmic bytes of one int4 weight-only GEMM launch"""
     return n * k // 2 + (k // g) * n * 4 + m * k * 2 + m * n * 2
 
 
@@ -316,7 +316,7 @@ def time_mega_kernel(eng, iters):
 
 
 def time_reference_gpu_kernels(quant, group_size, shapes, n_layer, iters, device):
-    """The reference's own GPU kernel on the same shapes, same run (BASELINE.md section 2): for int4
+    """The reference's own GPU kernel on the same shapes, same run: for int4
     aten._weight_int4pack_mm on weights packed by aten._convert_weight_to_int4pack(inner_k_tiles=8)
     (tensor_core_tiled_layout.py:104,279); for int8 the eager formula mm(x, w.t().to(bf16)) * scale (plain_layout.py:256-262).
     One CUDA graph per shape over `n_layer` DISTINCT weights (> L2 in total), M = 1, CUDA events."""

@@ -1,4 +1,4 @@
-"""Throughput of the quantize / pack / unpack / dequant kernels (SURVEY.md section 8 rows a3-a6, a12, a13) against the
+"""Throughput of the quantize / pack / unpack / dequant kernels against the
 HBM roofline, next to the reference's eager op sequence on the same GPU.
 Algorithmic bytes: int4 quantize+pack 2NK (read) + NK/2 + (K/G) N 4 (write); int8 quantize 2NK + NK + 2N;
 unpack NK/2 -> 4NK; dequant NK/2 + qparams -> 2NK.

@@ -2,7 +2,7 @@
  * ao_b200.h — C ABI of libao_b200.so: B200 (sm_100a) kernels for torchao's
  * weight-only quantized linear path.
  *
- * Boundary rules (mirror SURVEY.md §8(b)):
+ * Boundary rules:
  *   - plain pointers + sizes + cudaStream_t (passed as void*); no torch / ATen types;
  *   - every pointer is a DEVICE pointer on the current CUDA device unless noted;
  *   - the library never allocates, frees, synchronises or retains pointers: all
@@ -209,7 +209,7 @@ AO_B200_API int ao_b200_int8_gemv_fused(const void* x, int64_t M, int64_t Kx, in
                             int epilogue, void* stream);
 
 /* ---------------------------------------------------------------- decode-step glue ---- */
-/* The non-GEMM remainder of one Llama decode step (SURVEY.md §8 a16 / N2; reference:
+/* The non-GEMM remainder of one Llama decode step (reference:
  * torchao/_models/llama/model.py).  All of them read the token position from DEVICE memory
  * (int32 *input_pos) so that one captured CUDA graph can be replayed for every token. */
 
@@ -283,7 +283,7 @@ AO_B200_API int ao_b200_silu_mul(const void* gate_up, void* out, int64_t B, int6
 AO_B200_API int ao_b200_sample(const void* logits, int64_t ldl, int64_t B, int64_t V, float temperature, int top_k,
                                const void* noise, int64_t ldq, void* next_tok, void* stream);
 
-/* ---- tensor-parallel exchange over NVLink peer memory (new: the reference has no int4 TP path; SURVEY.md section 8e
+/* ---- tensor-parallel exchange over NVLink peer memory (new: the reference has no int4 TP path
  * names the collective it replaces: ncclAllReduce(sum, bf16) of [B][dim] after the row-parallel wo and w2) ------------
  * One process per GPU.  Every rank allocates ONE exchange buffer with ao_b200_tp_alloc (cudaMalloc, zeroed; returns the
  * 64-byte CUDA IPC handle), hands the handle to its peers (any host channel), and opens theirs with ao_b200_tp_open.

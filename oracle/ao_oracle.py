@@ -284,7 +284,7 @@ def unpack_tinygemm(packed, inner_k_tiles=8):
     return q
 
 
-# ---- the B200 strip-major layout (this build's own; see DESIGN.md "Data layout in HBM") ----
+# ---- the B200 strip-major layout (this build's own) ----
 # packed uint32 [N/16][K/64][32][4]: strip s (16 rows) x k-tile kt (64 k) = one 512-byte sub-tile; all sub-tiles of a
 # strip are contiguous.  In a sub-tile lane l=(g=l>>2, c=l&3) owns 16 bytes; word j:
 #   row = 16*s + g + 8*(j&1);  k0 = 64*kt + 32*(j>>1) + 8*c;  the word holds k0..k0+7 (nibble order of _pack_words).
@@ -338,7 +338,7 @@ def unpack_scales_and_zeros_b200(sz):
 # --------------------------------------------------------------------------
 def int4_weight_only_mm(x, q, scale, zero, group_size):
     """y[m][n] = bf16( sum_k fp32(x[m][k] * W'[n][k]) ), W' = dequantize_tinygemm.
-    Semantics of aten._weight_int4pack_mm (SURVEY.md §8 a10); summation order is
+    Semantics of aten._weight_int4pack_mm; summation order is
     unspecified there, here it is float64 (tolerance-compared, not bit-compared)."""
     wd = dequantize_tinygemm(q, scale, zero, group_size).astype(np.float64)
     return bf16_round((x.astype(np.float64) @ wd.T).astype(F32))

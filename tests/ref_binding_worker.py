@@ -1,5 +1,5 @@
 """The drop-in boundary on the REAL reference package: imports the unmodified reference (oracle/_ref), applies the edit
-INTEGRATION.md describes — ctypes-load libao_b200.so, CUDA backends for the reference's own
+the integration guide describes — ctypes-load libao_b200.so, CUDA backends for the reference's own
 `torchao::unpack_tensor_core_tiled_layout` / `dequantize_tensor_core_tiled_layout` schemas (torchao/ops.py:16-21), the
 int4 layout's `from_plain` and linear impl routed to the strip-major kernels — and then runs the checks of the
 reference's own tests (restated from /root/reference/test/test_ops.py:282-467, which does not travel to the GPU box)
@@ -53,7 +53,7 @@ def bind(lib_path):
     impl.impl("unpack_tensor_core_tiled_layout", unpack_cuda, "CUDA")
     impl.impl("dequantize_tensor_core_tiled_layout", dequant_cuda, "CUDA")
 
-    # ---- the int4 layout routed to the strip-major kernels (INTEGRATION.md section 3)
+    # ---- the int4 layout routed to the strip-major kernels
     from torchao.dtypes.affine_quantized_tensor_ops import _AQT_QLINEAR_DISPATCH_TABLE
     from torchao.dtypes.uintx import tensor_core_tiled_layout as tctl
 

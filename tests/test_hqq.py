@@ -1,4 +1,4 @@
-"""Int4WeightOnlyConfig(use_hqq=True) on the GPU (csrc/hqq.cu, SURVEY.md section 8 N1) against the reference's golden
+"""Int4WeightOnlyConfig(use_hqq=True) on the GPU (csrc/hqq.cu) against the reference's golden
 vectors (tests/golden/hqq_*.npz, produced by _choose_qparams_and_quantize_affine_hqq on CPU) and the numpy oracle.
 The solver iterates in fp32 with a mean over each group, so agreement is stated as a tolerance: scale bit-exact (no
 iteration in it), q identical on >= 99.9 % of the weights and never off by more than one step, zero within a bf16 ulp

@@ -153,7 +153,7 @@ def test_int8_b200_layout_round_trip_and_word_contract():
 
 
 # ------------------------------------------------------------------------------------------------
-# HQQ (SURVEY.md section 8 N1): tolerance-pinned, see the docstring of ao_oracle.hqq_quantize
+# HQQ: tolerance-pinned, see the docstring of ao_oracle.hqq_quantize
 # ------------------------------------------------------------------------------------------------
 HQQ = sorted(glob.glob(os.path.join(GOLDEN, "hqq_*.npz")))
 

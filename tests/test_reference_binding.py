@@ -1,6 +1,6 @@
 """The boundary proved on the real reference package:
 tests/ref_binding_worker.py imports the unmodified reference from oracle/_ref, binds libao_b200.so into it exactly as
-INTEGRATION.md prescribes and runs the reference's own checks (test/test_ops.py:282-496 restated: the reference's test
+the integration guide prescribes and runs the reference's own checks (test/test_ops.py:282-496 restated: the reference's test
 tree does not travel to the GPU box) — unpack bit-exact, dequant identical to the aten identity-matmul, opcheck with all
 FOUR utilities (incl. test_aot_dispatch_dynamic), quantize_ + linear with the reference's dispatch routed to the
 strip-major kernels."""

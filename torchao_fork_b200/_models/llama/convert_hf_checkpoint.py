@@ -1,6 +1,6 @@
 """HuggingFace Llama checkpoint -> the gpt-fast `model.pth` this package (and the reference) loads.
 
-Counterpart of /root/reference/scripts/convert_hf_checkpoint.py:20-139 (real-checkpoint path).  Three
+Counterpart of /root/reference/scripts/convert_hf_checkpoint.py:20-139 (the real-checkpoint path).  Three
 things happen to the tensors:
 
   * names: `model.layers.N.self_attn.q_proj.weight` -> `layers.N.attention.wq.weight` etc. (table below);

@@ -237,7 +237,7 @@ def _random_init_model(name, device, precision):
 
 def apply_quantization(model, quantization: Optional[str]):
     """`-q` of the reference CLI (generate.py:395-428), the techniques on this path: int8wo, int4wo-<groupsize>,
-    int4wo-<groupsize>-hqq.  Everything else the reference lists is outside SURVEY.md §8 and says so."""
+    int4wo-<groupsize>-hqq.  Everything else the reference lists is outside this package's scope and says so."""
     from ... import Int4WeightOnlyConfig, Int8WeightOnlyConfig, quantize_
     if not quantization:
         return model

@@ -1,6 +1,6 @@
 """gpt-fast style Llama used by the decode benchmark — host-side mirror of the reference's
 torchao/_models/llama/model.py (same module / parameter names, so `quantize_` walks it identically and
-state dicts interchange).  This eager module is the *caller* of the quantized linears (SURVEY.md §8 a16):
+state dicts interchange).  This eager module is the *caller* of the quantized linears:
 it runs prefill; single-token decode goes through DecodeEngine (decode_engine.py), which drives the same
 weights through the CUDA decode kernels inside one CUDA graph.
 """
@@ -52,7 +52,7 @@ class ModelArgs:
 
 
 _L3 = dict(n_local_heads=8, vocab_size=128256, rope_base=500000)
-# reference: model.py:75-158.  "Llama-3-70B" is the harness's addition (SURVEY.md §8): the reference only
+# reference: model.py:75-158.  "Llama-3-70B" is the harness's addition: the reference only
 # has "70B" (Llama-2 vocab) and "Llama-3.1-70B" (scaled rope); BASELINE.json config 4 names Llama-3-70B.
 transformer_configs = {
     "CodeLlama-7b-Python-hf": dict(block_size=16384, vocab_size=32000, n_layer=32, dim=4096, rope_base=1000000),

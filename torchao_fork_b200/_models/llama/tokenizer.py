@@ -1,6 +1,6 @@
 """Tokenizers for the gpt-fast Llama: sentencepiece (Llama-2 family) and tiktoken BPE (Llama-3 family).
 
-Counterpart of /root/reference/torchao/_models/llama/tokenizer.py:13-126 (SURVEY.md §8f N4: what `generate.py` / `eval.py`
+Counterpart of /root/reference/torchao/_models/llama/tokenizer.py:13-126 (what `generate.py` / `eval.py`
 put in front of the hot path).  Same surface: `encode(text) -> list[int]`, `decode(ids) -> str`, `bos_id()`, `eos_id()`,
 and `get_tokenizer(path, model_name)` picking the tiktoken one when the model name says "Llama-3".
 

@@ -4,7 +4,7 @@ one NVSwitch box, one process per GPU, an all-reduce only after the two row-para
 The reference has no working equivalent for int4: its DTensor TP test of Int4WeightOnlyConfig is skipped
 (test/dtypes/test_affine_quantized_tensor_parallel.py:153-158), and torchao/_models/llama has no tp.py.  The
 partitioning is the Megatron / gpt-fast one, applied to the bf16 weights BEFORE quantize_, so every rank quantizes its
-own shard and quantization groups never straddle a shard boundary (SURVEY.md section 8e):
+own shard and quantization groups never straddle a shard boundary:
 
   column-parallel (split output rows N): wqkv — by head groups: rank r takes q heads [r H/tp, (r+1) H/tp) and kv heads
       [r Hkv/tp, (r+1) Hkv/tp) out of the fused [q|k|v] rows (model.py:422-424); w1, w3; output (vocab rows, logits

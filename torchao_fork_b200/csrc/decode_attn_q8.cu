@@ -1,4 +1,4 @@
-// Attention.forward for one new token over an int8 KV cache (SURVEY.md §8 N2): the decode-side of
+// Attention.forward for one new token over an int8 KV cache: the decode-side of
 // AffineQuantizedKVCache (torchao/_models/llama/model.py:198-240).  One launch does
 //   RoPE on q and the new k (model.py:547-559),
 //   update(): q_k, k_scale = _quantize_activation_per_token_absmax(k) (torchao/quantization/utils.py:152-182) stored at

@@ -1,4 +1,4 @@
-// Non-GEMM remainder of one Llama decode step (SURVEY.md §8 a16 / N2): fused residual-add + RMSNorm,
+// Non-GEMM remainder of one Llama decode step: fused residual-add + RMSNorm,
 // RoPE + KV-cache append, GQA decode attention, SiLU*mul.  All read the token position from DEVICE
 // memory so a captured CUDA graph can be replayed for every token.
 #include <mutex>

@@ -5,7 +5,7 @@
 //
 // i.e. the affine dequant (q-8)*s+z is applied ONCE PER GROUP in fp32 to the tensor-core partial sum instead of
 // once per weight in bf16 (that is the arithmetic of the reference's CPU op _weight_int4pack_mm_for_cpu, which
-// dequantises in fp32 without rounding W' to bf16 — SURVEY.md §8 a15; the CUDA op rounds W' to bf16 first, a10;
+// dequantises in fp32 without rounding W' to bf16; the CUDA op rounds W' to bf16 first;
 // the two differ by the bf16 rounding of each W', well inside the stated GEMM tolerance).  What is left per packed
 // word is 3 shifts + 4 lop3 (nibble -> bf16 value 128+q with the 0x4300 magic) + one mma.sync: half the issue
 // slots of the exact per-weight bf16 fma, which is what made v2 ALU-bound at ~54 % of HBM peak.

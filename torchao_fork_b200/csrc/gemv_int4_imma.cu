@@ -14,7 +14,7 @@
 //         y[col] += s_g * acc[col] + (z_g - 8 s_g) * S[col],   S[col] = sum of the limb over the segment,
 //     and the limbs are recombined (65536 a + 256 b + c) once per strip in the epilogue warp.  A warp's share of a stage
 //     is 128 k: one segment at G >= 128 (G = 256: two warps share a group's scale / zero), two at G = 64, four at G = 32.
-// Arithmetic: fp32-dequant semantics (SURVEY.md section 8 a15), like gemv_int4_fused.cu; the products are exact integers.
+// Arithmetic: fp32-dequant semantics, like gemv_int4_fused.cu; the products are exact integers.
 #include <cstdlib>
 
 #include "common.cuh"

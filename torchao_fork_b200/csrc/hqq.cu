@@ -1,4 +1,4 @@
-// HQQ (half-quadratic quantization) qparam search for Int4WeightOnlyConfig(use_hqq=True) — SURVEY.md section 8 row N1.
+// HQQ (half-quadratic quantization) qparam search for Int4WeightOnlyConfig(use_hqq=True).
 //
 // Reference: torchao/quantization/quant_primitives.py:1998-2111 (_choose_qparams_and_quantize_affine_hqq) with
 // optimize_weights_proximal_legacy (:1915-1973) and _convert_to_affinequantized_format (:1981-1995), called from

@@ -172,7 +172,7 @@ class AffineQuantizedTensor(torch.Tensor):
             return cls(tensor_impl, block_size, original_shape, quant_min, quant_max, zero_point_domain,
                        dtype=input_float.dtype)
 
-        raise NotImplementedError(f"layout {_layout} is outside the B200 hot path (SURVEY.md §8)")
+        raise NotImplementedError(f"layout {_layout} is outside the B200 hot path")
 
     # ------------------------------------------------------------------ views of the data
     @property

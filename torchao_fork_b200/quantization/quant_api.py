@@ -153,7 +153,7 @@ def _int4_weight_only_transform(module, config):
 class Float8DynamicActivationInt4WeightConfig(AOBaseConfig):
     """reference: quant_api.py:1159-1197 — float8 per-row DYNAMIC ACTIVATION quantization on top of preshuffled int4
     weights (fbgemm's Int4PreshuffledTensor and its fp8 x int4 kernel).  The config exists so that code naming it imports;
-    applying it raises: it is not a weight-only path (the activations are quantized too), outside SURVEY.md section 8."""
+    applying it raises: it is not a weight-only path (the activations are quantized too), outside this package's scope."""
 
     packing_format: PackingFormat = PackingFormat.PRESHUFFLED
 

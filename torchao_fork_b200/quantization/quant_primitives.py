@@ -3,7 +3,7 @@
 Same names, argument meaning and error behaviour as torchao/quantization/quant_primitives.py for
 the two branches the weight-only path uses (tinygemm uint4 group-wise; symmetric int8 per-row).
 Everything else in the reference file (HQQ, float8, floatx, GGUF, QQQ ...) is outside the hot
-path (SURVEY.md §8) and raises NotImplementedError rather than silently taking a slow path.
+path and raises NotImplementedError rather than silently taking a slow path.
 
 The arithmetic contract is the reference's eager bf16 arithmetic: every op rounds to bf16.
 `CUDA_DIV_SEMANTICS` selects how `tensor / python_scalar` is evaluated: torch CUDA eager
