@@ -451,6 +451,42 @@ def _check_batches(dtype, name):
     assert _err(l3, torch.stack([ref["d"][-1], ref["a"][-1], ref["c"][-1]])) < tol
 
 
+def _uneven_config():
+    """Every layer with sizes and constants of its own: head counts and sizes, latent sizes, partial rotation with its own
+    base, scales, expert counts / sizes / limits, with and without a shared expert, one layer without feed-forward,
+    borrowing layers whose heads differ from the lender's."""
+    cfg = O.random_config(width=96, vocab=113, heads=4, dim=16, rot_dim=16, vdim=32, kv_rank=64, n_layers=5,
+                          share=(None, 0, None, None, 3), experts=6, top=2, ff=24, shared_ff=16, no_mlp=(3,))
+    L = cfg["layers"]
+    L[1]["mixer"].update(heads=6, dim=8, vdim=48, scale=0.27)
+    L[1]["mlp"] = {"expert": {"ff": 8, "limit": 2.0}, "kind": "moe", "router": {"experts": 9, "top": 4},
+                   "shared": {"ff": 40, "limit": 3.0}}
+    L[2]["mixer"].update(heads=2, dim=32, vdim=16, kv_rank=40, rot_dim=8, scale=0.31, rot={"base": 777.0, "dims": 4})
+    L[2]["mlp"] = {"expert": {"ff": 16, "limit": 0.8}, "kind": "moe", "router": {"experts": 3, "top": 3}}
+    L[3]["mixer"].update(heads=1, dim=16, vdim=64, kv_rank=128, rot_dim=32, scale=0.2, rot={"base": 50.0, "dims": 32})
+    L[4]["mixer"].update(heads=3, dim=32, vdim=16, kv_rank=128, rot_dim=32, scale=0.15, rot={"base": 50.0, "dims": 32})
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layers_of_unequal_sizes_whole_portions_and_decoding(dtype):
+    cfg = _uneven_config()
+    w = O.random_weights(cfg, seed=21)
+    toks = _tokens(cfg, 90, 9)
+    ref = O.forward(cfg, w, toks)
+    tol = F32_TOL if dtype == torch.float32 else _bf16_tol(cfg, w, toks)
+    m = _model(cfg, w, dtype)
+    eng, st = m.step_engine, m.states
+    for cuts in ([90], [70] + [1] * 20, [40, 2, 33, 3, 12]):
+        slot = st.slot_of("r")
+        outs, at = [], 0
+        for k in cuts:
+            outs.append(eng.step([(slot, toks[at:at + k])], "all"))
+            at += k
+        st.release("r")
+        assert _err(torch.cat(outs), ref) < tol, cuts
+
+
 def test_rotation_and_keys_far_away_in_the_model():
     """A sequence of several hundred tokens through portions and single tokens: positions far from zero, keys far back."""
     cfg = O.random_config(width=48, vocab=61, heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=24, n_layers=2, share=(None, 0),
