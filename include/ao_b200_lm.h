@@ -95,6 +95,9 @@ AO_B200_API int ao_lm_latent_attention_expanded(const void* qn, const float* qr,
  * index) -> idx[t][top], weight[t][top] = their scores, not renormalised. */
 AO_B200_API int ao_lm_router_topk(const void* h, const void* w_router, int dt, int64_t n, int64_t width, int E, int top,
                                   int32_t* idx, float* weight, void* stream);
+/* The same choice from fp32 logits[n][E] that a GEMM has made (prompt portions). */
+AO_B200_API int ao_lm_router_topk_logits(const float* logits, int64_t n, int E, int top, int32_t* idx, float* weight,
+                                         void* stream);
 
 /* Clipped GLU: g = min(a, limit), u = clamp(b, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1).
  *   ao_lm_glu_act: gu[n][2 ff] = (a | b) -> y[n][ff].

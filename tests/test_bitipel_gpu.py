@@ -296,6 +296,14 @@ def test_router_kernel_softmax_over_all_then_top(E, top, W):
     assert torch.equal(idx.cpu().long(), ri)
     assert torch.allclose(wt.double().cpu(), rw, rtol=1e-5, atol=1e-7)
     assert top == E or float(wt.sum(-1).max()) < 1.0       # scores of the chosen, not renormalised
+    # the same choice from logits that a GEMM made (what prompt portions use); 19 tokens: more than one CTA of warps
+    h2 = torch.randn(19, W, generator=g).to(torch.bfloat16)
+    z = (h2.double() @ wr.double().T).float().cuda()
+    idx2 = torch.empty(19, top, dtype=torch.int32, device="cuda")
+    wt2 = torch.empty(19, top, device="cuda")
+    lib.lm_check(L.ao_lm_router_topk_logits(z.data_ptr(), 19, E, top, idx2.data_ptr(), wt2.data_ptr(), _st()), "router_logits")
+    rw, ri = O.route(h2.double(), wr, top)
+    assert torch.equal(idx2.cpu().long(), ri) and torch.allclose(wt2.double().cpu(), rw, rtol=1e-5, atol=1e-7)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -317,6 +325,22 @@ def test_expert_kernels_and_sorted_path_against_oracle(dtype):
     # the clip matters in this test: some pre-activations exceed the limits
     pre = x.double() @ w["l0.mlp.e0.gate"].double().T
     assert float(pre.max()) > 0.8
+
+
+@pytest.mark.parametrize("ff", [24, 17, 128])
+def test_clipped_glu_activation_kernel_vector_and_scalar_rows(ff):
+    """g = min(a, limit), u = clamp(b, +-limit), y = g sigmoid(1.702 g) (u + 1) on rows [a | b]; rows of 8k numbers take the
+    16-byte path, others the scalar one."""
+    lib, L = _lm()
+    g = torch.Generator().manual_seed(9)
+    gu = (torch.randn(11, 2 * ff, generator=g) * 2.0).to(torch.bfloat16)
+    y = torch.empty(11, ff, dtype=torch.bfloat16, device="cuda")
+    gud = gu.cuda()
+    lib.lm_check(L.ao_lm_glu_act(gud.data_ptr(), lib.DT_BF16, 11, ff, 1.25, 1.702, y.data_ptr(), _st()), "glu_act")
+    a, b = gu[:, :ff].double().clamp(max=1.25), gu[:, ff:].double().clamp(-1.25, 1.25)
+    ref = a * torch.sigmoid(1.702 * a) * (b + 1.0)
+    assert torch.allclose(y.double().cpu(), ref, rtol=1e-2, atol=1e-2)
+    assert float(gu[:, :ff].max()) > 1.25 and float(gu[:, ff:].min()) < -1.25      # both clips were active
 
 
 def test_argmax_kernel_first_of_ties():

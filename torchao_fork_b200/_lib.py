@@ -144,6 +144,7 @@ LM_SIGNATURES = {
     "ao_lm_latent_attention_expanded": [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32,
                                         _i32, _i32, _f32, _vp, _vp, _vp, _vp],
     "ao_lm_router_topk": [_vp, _vp, _i32, _i64, _i64, _i32, _i32, _vp, _vp, _vp],
+    "ao_lm_router_topk_logits": [_vp, _i64, _i32, _i32, _vp, _vp, _vp],
     "ao_lm_glu_act": [_vp, _i32, _i64, _i64, _f32, _f32, _vp, _vp],
     "ao_lm_expert_gate_up": [_vp, _vp, _vp, _i32, _vp, _i64, _i32, _i64, _i64, _i64, _f32, _f32, _vp, _vp],
     "ao_lm_expert_down": [_vp, _vp, _i32, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _vp, _vp],

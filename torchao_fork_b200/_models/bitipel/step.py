@@ -291,7 +291,11 @@ class StepEngine:
         tdt = self.m.dtype
         ridx = torch.empty(n, f.top, dtype=torch.int32, device=dev)
         rwt = torch.empty(n, f.top, dtype=torch.float32, device=dev)
-        _lib.lm_check(L.ao_lm_router_topk(_p(xc), _p(lay.router), dt, n, W, f.experts, f.top, _p(ridx), _p(rwt), st), "router_topk")
+        if gemv or f.experts > 1024:
+            _lib.lm_check(L.ao_lm_router_topk(_p(xc), _p(lay.router), dt, n, W, f.experts, f.top, _p(ridx), _p(rwt), st), "router_topk")
+        else:   # many tokens: the logits as one GEMM with an fp32 result, then softmax and choice per token
+            z = torch.mm(xc, lay.router.t(), out_dtype=torch.float32) if tdt == torch.bfloat16 else torch.mm(xc, lay.router.t())
+            _lib.lm_check(L.ao_lm_router_topk_logits(_p(z), n, f.experts, f.top, _p(ridx), _p(rwt), st), "router_topk_logits")
         esz = lay.wgu.element_size()
         if gemv:
             if f.shared_ff:

@@ -12,6 +12,34 @@ namespace {
 
 constexpr int kWarps = 8;
 
+// one warp: scores = softmax over z[0..E) (shared memory, destroyed), then the `top` largest as they are (ties: lowest index)
+__device__ __forceinline__ void softmax_topk(float* z, int E, int top, int lane, int32_t* idx_out, float* weight_out) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float den = 0.f;
+  for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
+  den = warp_sum(den);
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = E;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) best = z[e], at = e;          // ascending e: the lowest index wins inside a lane
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
+    }
+    if (lane == 0) {
+      idx_out[k] = at;
+      weight_out[k] = expf(best - mx) / den;
+    }
+    __syncwarp();
+    if (lane == 0 && at < E) z[at] = -INFINITY;
+    __syncwarp();
+  }
+}
+
 // one CTA per token: E dot products (a warp each, round robin), then warp 0 does softmax + top-k.  A step of few tokens
 // has few CTAs: each then runs 32 warps, so that one token's router matrix is read by more loads in flight.
 template <typename T>
@@ -51,30 +79,20 @@ __global__ void __launch_bounds__(1024) router_topk_kernel(const T* __restrict__
   }
   __syncthreads();
   if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float den = 0.f;
-  for (int e = lane; e < E; e += 32) den += expf(z[e] - mx);
-  den = warp_sum(den);
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int at = E;
-    for (int e = lane; e < E; e += 32)
-      if (z[e] > best) best = z[e], at = e;          // ascending e: the lowest index wins inside a lane
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
-      if (ov > best || (ov == best && oi < at)) best = ov, at = oi;
-    }
-    if (lane == 0) {
-      idx[t * top + k] = at;
-      weight[t * top + k] = expf(best - mx) / den;
-    }
-    __syncwarp();
-    if (lane == 0 && at < E) z[at] = -INFINITY;
-    __syncwarp();
-  }
+  softmax_topk(z, E, top, lane, idx + t * top, weight + t * top);
+}
+
+// one warp per token over logits a GEMM has made (prompt portions: the router matrix is read once, not once per token)
+__global__ void router_topk_logits_kernel(const float* __restrict__ logits, int64_t n, int E, int top,
+                                          int32_t* __restrict__ idx, float* __restrict__ weight) {
+  extern __shared__ float sm[];   // [kWarps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * kWarps + warp;
+  if (t >= n) return;
+  float* z = sm + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[t * E + e];
+  __syncwarp();
+  softmax_topk(z, E, top, lane, idx + t * top, weight + t * top);
 }
 
 // grid (ceil(ff / 8), pairs): a warp computes one row of both projections of its pair's expert
@@ -199,6 +217,15 @@ extern "C" int ao_lm_router_topk(const void* h, const void* w_router, int dt, in
     kern<<<(unsigned)n, (n <= 64 ? 32 : kWarps) * 32, smem, lm_stream(stream)>>>(static_cast<const T*>(h), static_cast<const T*>(w_router), width,
                                                                E, top, idx, weight);
   });
+  return lm_launch_status();
+}
+
+extern "C" int ao_lm_router_topk_logits(const float* logits, int64_t n, int E, int top, int32_t* idx, float* weight, void* stream) {
+  LM_CHECK_ARG(logits && idx && weight && n > 0 && E > 0 && top > 0 && top <= E);
+  const size_t smem = (size_t)kWarps * E * sizeof(float);
+  if (smem > 48 * 1024) return AO_B200_ERR_UNSUPPORTED;
+  router_topk_logits_kernel<<<(unsigned)((n + kWarps - 1) / kWarps), kWarps * 32, smem, lm_stream(stream)>>>(logits, n, E, top, idx,
+                                                                                                           weight);
   return lm_launch_status();
 }
 

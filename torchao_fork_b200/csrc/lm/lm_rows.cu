@@ -148,6 +148,31 @@ __global__ void glu_act_kernel(const T* __restrict__ gu, int64_t n, int64_t ff, 
   stf(y + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
 }
 
+// bf16 rows with ff a multiple of 8: one thread makes 8 outputs from two 16-byte loads
+__global__ void glu_act_vec_kernel(const __nv_bfloat16* __restrict__ gu, int64_t n, int64_t ff, float limit, float alpha,
+                                   __nv_bfloat16* __restrict__ y) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, per = ff / 8;
+  if (i >= n * per) return;
+  const int64_t t = i / per, f = (i - t * per) * 8;
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(gu + t * 2 * ff + f));
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(gu + t * 2 * ff + ff + f));
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float r[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float gv = fminf(__uint_as_float(e ? aw[j] & 0xFFFF0000u : aw[j] << 16), limit);
+      const float uv = fminf(fmaxf(__uint_as_float(e ? bw[j] & 0xFFFF0000u : bw[j] << 16), -limit), limit);
+      r[e] = gv / (1.f + expf(-alpha * gv)) * (uv + 1.f);
+    }
+    const __nv_bfloat162 pk = __floats2bfloat162_rn(r[0], r[1]);
+    o[j] = *reinterpret_cast<const uint32_t*>(&pk);
+  }
+  *reinterpret_cast<uint4*>(y + t * ff + f) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <typename T>
 __global__ void add_cast_kernel(const T* __restrict__ b, int64_t count, float* __restrict__ a) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -250,6 +275,11 @@ extern "C" int ao_lm_latent_prep(const void* proj, int dt, int64_t ld, int64_t n
 
 extern "C" int ao_lm_glu_act(const void* gu, int dt, int64_t n, int64_t ff, float limit, float alpha, void* y, void* stream) {
   LM_CHECK_ARG(gu && y && n > 0 && ff > 0);
+  if (dt == AO_LM_BF16 && ff % 8 == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+    glu_act_vec_kernel<<<(unsigned)((n * (ff / 8) + 255) / 256), 256, 0, lm_stream(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gu), n, ff, limit, alpha, static_cast<__nv_bfloat16*>(y));
+    return lm_launch_status();
+  }
   const unsigned grid = (unsigned)((n * ff + 255) / 256);
   LM_DISPATCH(dt, glu_act_kernel<T><<<grid, 256, 0, lm_stream(stream)>>>(static_cast<const T*>(gu), n, ff, limit, alpha,
                                                                          static_cast<T*>(y)));
