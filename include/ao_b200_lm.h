@@ -126,6 +126,88 @@ AO_B200_API int ao_lm_add_cast(const void* b, int dt, int64_t count, float* a_in
 /* greedy choice: out[b] = index of the largest of logits[b][0..V) (first one on ties) */
 AO_B200_API int ao_lm_argmax(const float* logits, int64_t ld, int64_t B, int64_t V, int64_t* out, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Residual kept as n_streams fp32 copies per token, x[t][s][width] (one stream: the ordinary residual), recurrent
+ * mixers with per-slot state, attention over chunks with a ring cache.  Rows of a step are runs ("segments") of
+ * consecutive positions of one sequence: back[t] = rows of the same segment in front of row t, ahead[t] = behind it.
+ */
+
+/* x[t][s][:] = table[tok[t]][:] * scale + sinusoid(pos[t]) for every stream s; coordinate 2i of the sinusoid is
+ * sin(pos * freq[i]), 2i+1 the cosine (freq: width / 2 rounded up doubles; the angle is reduced in double). */
+AO_B200_API int ao_lm_embed_sinusoid(const void* table, int dt, const int64_t* tok, const int32_t* pos, int64_t n,
+                                     int64_t width, float scale, const double* freq, int n_streams, float* x, void* stream);
+
+/* Read-out + norm: u = sum_s coef_in[s] x[r][s] (coef_in == null: plain sum), out[i] = u / sqrt(mean(u^2) + eps) *
+ * (weight_offset + weight[:]) for r = rows ? rows[i] : i, i < m.  Written as fp32 (out_f32) and / or in `dt` (out). */
+AO_B200_API int ao_lm_streams_norm(const float* x, const int32_t* rows, int64_t m, int n_streams, int64_t width,
+                                   const void* coef_in, const void* weight, int dt, float weight_offset, float eps,
+                                   float* out_f32, void* out, void* stream);
+
+/* Write-back: x[t][d] <- sum_s mix[s][d] x[t][s] + coef_out[d] * y[t], all streams from the old ones (mix == null:
+ * identity; coef_out == null: ones; y in y_dt).  With conv_state: rows with ahead == 0 also move the last taps - 1 rows
+ * of conv_in (fp32 [n][width]) into conv_state[slot][taps - 1][width], the memory of ao_lm_causal_conv. */
+AO_B200_API int ao_lm_streams_update(float* x, const void* y, int y_dt, int64_t n, int n_streams, int64_t width,
+                                     const void* mix, const void* coef_out, int dt, const float* conv_in, float* conv_state,
+                                     int taps, const int32_t* slot, const int32_t* back, const int32_t* ahead, void* stream);
+
+/* y[t][c] = gelu_tanh(gu[t][c]) * gu[t][ff + c] */
+AO_B200_API int ao_lm_gelu_glu(const void* gu, int dt, int64_t n, int64_t ff, void* y, void* stream);
+
+/* Causal convolution over time per channel: v(t) = x[t][c] + in_bias[c];
+ * y[t][c] = (residual ? v(t) : 0) + out_bias[c] + sum_j kernel[c][j] * v(t - (taps - 1 - j)).  Inputs in front of the
+ * step come from state[slot][taps - 1][channels] (oldest first, bias included), inputs in front of position 0 are zero.
+ * The kernel does not write the state: ao_lm_streams_update / ao_lm_rglru_scan do, after every reader has run. */
+AO_B200_API int ao_lm_causal_conv(const float* x, int64_t ldx, const void* in_bias, int64_t n, int64_t channels, int taps,
+                                  const void* kernel, const void* out_bias, int dt, int residual, const float* state,
+                                  const int32_t* slot, const int32_t* pos, const int32_t* back, float* out_f32, void* out,
+                                  void* stream);
+
+/* Gated linear recurrences S_t = a_t S_(t-1) + b_t per channel, state[slot][channels] fp32 (read unless the segment
+ * starts at position 0, written with the segment's last S).  tile_first / tile_count: runs of rows of ONE segment.
+ * seg_tile0 == null: every tile is a whole segment (one launch).  Otherwise segment k owns tiles seg_tile0[k] ..
+ * + seg_tiles[k] - 1 and the scan takes three launches (tile summaries, carries, rows) with a workspace of
+ * ao_lm_scan_workspace_bytes.
+ *   mingru: z = sigmoid(proj[t][z_off + c] + z_bias[c]), u = proj[t][x_off + c] + x_bias[c], cand = u + 1/2 (u >= 0) |
+ *           sigmoid(u); a = 1 - z, b = z * cand;  out[t][c] = out_scale * S_t * silu(proj[t][g_off + c]).
+ *   rglru:  gates[block][t][2 bw] = (r | i) pre-activations of the block's bw channels; r = sigmoid(. + r_bias),
+ *           i = sigmoid(. + i_bias); log a = -decay * r * softplus(lam[c]); b = sqrt(1 - a^2) * i * u[t][c];
+ *           out[t][c] = S_t * gelu_tanh(y_pre[t][c] + y_bias[c]).  With conv_state, the segment's last rows of
+ *           conv_x (+ conv_in_bias) become the memory of the convolution that produced u. */
+AO_B200_API int64_t ao_lm_scan_workspace_bytes(int n_tiles, int64_t channels);
+AO_B200_API int ao_lm_mingru_scan(const float* proj, int64_t ld, int64_t z_off, int64_t x_off, int64_t g_off, const void* z_bias,
+                                  const void* x_bias, int dt, int64_t channels, float* state, const int32_t* slot,
+                                  const int32_t* pos, const int32_t* back, const int32_t* tile_first, const int32_t* tile_count,
+                                  int n_tiles, const int32_t* seg_tile0, const int32_t* seg_tiles, int n_segments,
+                                  float* workspace, float out_scale, void* out, int64_t ld_out, void* stream);
+AO_B200_API int ao_lm_rglru_scan(const float* gates, int64_t n, int block_width, const void* r_bias, const void* i_bias,
+                                 const void* lam, float decay, const float* u, const float* y_pre, int64_t ld_y,
+                                 const void* y_bias, int dt, int64_t channels, float* state, const float* conv_x,
+                                 int64_t conv_ld, const void* conv_in_bias, float* conv_state, int taps, const int32_t* slot,
+                                 const int32_t* pos, const int32_t* back, const int32_t* tile_first, const int32_t* tile_count,
+                                 int n_tiles, const int32_t* seg_tile0, const int32_t* seg_tiles, int n_segments,
+                                 float* workspace, void* out, void* stream);
+
+/* Attention over chunks of `chunk` positions (a query sees the keys of its own chunk up to itself), H query heads over
+ * G key/value heads.  ao_lm_qk_prep: unit-RMS queries (fp32 [n][H][d]) and keys (`dt` [n][G][d]) and the values in
+ * `dt` [n][G][dv] from an fp32 projection row.  ao_lm_chunk_attention:
+ *   score = softcap * tanh(scale * q.k / softcap) (softcap <= 0: none) + dist_bias[min(i - j, n_dist - 1)][head];
+ *   out[t][head * dv + c] = out_scale * softmax-weighted values * sigmoid(gate[t][head * dv + c]).
+ * Keys of earlier steps come from the ring (ring_k [slots][chunk][G][d], ring_v likewise; position p in row p % chunk),
+ * the step's own from kn / vn.  tile_first / tile_count: runs of <= tile_rows rows of one segment INSIDE one chunk
+ * (ao_lm_chunk_attention_plan gives tile_rows, 0 = shape not covered).  ao_lm_ring_append, after the attention, stores
+ * the step's rows that no later row of the step overwrites (ahead < chunk). */
+AO_B200_API int ao_lm_qk_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, int64_t n, int H, int G,
+                              int d, int dv, float eps, int dt, float* qn, void* kn, void* vn, void* stream);
+AO_B200_API int ao_lm_chunk_attention_plan(int dt, int H, int G, int d, int dv, int* tile_rows);
+AO_B200_API int ao_lm_chunk_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
+                                      int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
+                                      const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
+                                      const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk,
+                                      float scale, float softcap, float out_scale, void* out, int64_t ld_out, void* stream);
+AO_B200_API int ao_lm_ring_append(const void* kn, const void* vn, int64_t n, int64_t k_row, int64_t v_row, int ring, int dt,
+                                  const int32_t* slot, const int32_t* pos, const int32_t* ahead, void* ring_k, void* ring_v,
+                                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

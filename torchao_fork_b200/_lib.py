@@ -152,8 +152,23 @@ LM_SIGNATURES = {
     "ao_lm_scatter_add_rows": [_vp, _i32, _vp, _vp, _i32, _i64, _i64, _vp, _vp],
     "ao_lm_add_cast": [_vp, _i32, _i64, _vp, _vp],
     "ao_lm_argmax": [_vp, _i64, _i64, _i64, _vp, _vp],
+    "ao_lm_embed_sinusoid": [_vp, _i32, _vp, _vp, _i64, _i64, _f32, _vp, _i32, _vp, _vp],
+    "ao_lm_streams_norm": [_vp, _vp, _i64, _i32, _i64, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp],
+    "ao_lm_streams_update": [_vp, _vp, _i32, _i64, _i32, _i64, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp],
+    "ao_lm_gelu_glu": [_vp, _i32, _i64, _i64, _vp, _vp],
+    "ao_lm_causal_conv": [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ao_lm_scan_workspace_bytes": [_i32, _i64],
+    "ao_lm_mingru_scan": [_vp, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32,
+                          _vp, _f32, _vp, _i64, _vp],
+    "ao_lm_rglru_scan": [_vp, _i64, _i32, _vp, _vp, _vp, _f32, _vp, _vp, _i64, _vp, _i32, _i64, _vp, _vp, _i64, _vp, _vp, _i32,
+                         _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp],
+    "ao_lm_qk_prep": [_vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp],
+    "ao_lm_chunk_attention_plan": [_i32, _i32, _i32, _i32, _i32, _p32],
+    "ao_lm_chunk_attention": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                              _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
+    "ao_lm_ring_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
 }
-_LM_RESTYPES = {"ao_lm_latent_attention_workspace_bytes": _i64}
+_LM_RESTYPES = {"ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64}
 _lm = None
 _LM_ERRORS = {1: "invalid argument", 2: "unsupported shape", 3: "CUDA launch failed", 4: "workspace too small"}
 

@@ -1,6 +1,8 @@
 """Per-sequence memory of the models: key/value caches of the gpt-fast Llama (plain and int8), and the state of
 sequence models that keep something else per request — compressed (latent) keys, the previous token's input of a
-token-shift layer — in numbered slots that a host-side allocator hands out and takes back.
+token-shift layer, a ring of keys and values for attention that never looks past a fixed span, the state of a
+recurrence, the last inputs of a short convolution — in numbered slots that a host-side allocator hands out and takes
+back.
 """
 from typing import Dict, List, Optional
 
@@ -117,6 +119,53 @@ class TokenShiftState(nn.Module):
         new = torch.zeros(n_slots, self.prev.shape[1], dtype=torch.float32, device=self.prev.device)
         new[: self.prev.shape[0]] = self.prev
         self.prev = new
+
+
+def _grown(old: torch.Tensor, n_slots: int) -> torch.Tensor:
+    new = torch.zeros(n_slots, *old.shape[1:], dtype=old.dtype, device=old.device)
+    new[: old.shape[0]] = old
+    return new
+
+
+class RingKVCache(nn.Module):
+    """Keys and values of an attention that only ever reads the last `ring` positions or less (a chunked or a sliding
+    mask): position p of a sequence lives in row p % ring of its slot, k [slots][ring][kv_heads][dim] and
+    v [slots][ring][kv_heads][vdim].  What a sequence costs does not grow with its length."""
+
+    def __init__(self, n_slots, ring, kv_heads, dim, vdim, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        assert ring > 0
+        self.ring = ring
+        self.register_buffer("k", torch.zeros(n_slots, ring, kv_heads, dim, dtype=dtype, device=device))
+        self.register_buffer("v", torch.zeros(n_slots, ring, kv_heads, vdim, dtype=dtype, device=device))
+
+    def grow(self, n_slots):
+        self.k, self.v = _grown(self.k, n_slots), _grown(self.v, n_slots)
+
+
+class RecurrentState(nn.Module):
+    """The state of a per-channel recurrence, fp32 [slots][width]; a sequence starts from zeros (the kernels do not
+    read the slot at position 0, so a reused slot needs no clearing)."""
+
+    def __init__(self, n_slots, width, device=None):
+        super().__init__()
+        self.register_buffer("s", torch.zeros(n_slots, width, dtype=torch.float32, device=device))
+
+    def grow(self, n_slots):
+        self.s = _grown(self.s, n_slots)
+
+
+class ConvState(nn.Module):
+    """The last taps - 1 inputs of a causal convolution over time, fp32 [slots][taps - 1][channels], oldest first."""
+
+    def __init__(self, n_slots, taps, channels, device=None):
+        super().__init__()
+        assert taps >= 2
+        self.taps = taps
+        self.register_buffer("x", torch.zeros(n_slots, taps - 1, channels, dtype=torch.float32, device=device))
+
+    def grow(self, n_slots):
+        self.x = _grown(self.x, n_slots)
 
 
 class SequenceStates:

@@ -39,6 +39,9 @@ def _load_builtin():
     from .bitipel import model as _bitipel
     register(Family("bitipel", from_folder=_bitipel.Bitipel.from_checkpoint, from_name=_bitipel.Bitipel.from_name,
                     names=lambda: list(_bitipel.bitipel_configs)))
+    from .tadolix import model as _tadolix
+    register(Family("tadolix", from_folder=_tadolix.Tadolix.from_checkpoint, from_name=_tadolix.Tadolix.from_name,
+                    names=lambda: list(_tadolix.tadolix_configs)))
 
 
 def architecture_of(folder) -> str:
