@@ -106,7 +106,8 @@ def chunk_attention(h, w, pre, a, eps):
         for i in range(T):
             lo = (i // C) * C
             s = (k[lo:i + 1, kv] @ q[i, hd]) * a["scale"]
-            s = cap * torch.tanh(s / cap)
+            if cap:
+                s = cap * torch.tanh(s / cap)
             s = s + torch.stack([rel[distance_bucket(i - j, B, a["bias_max"]), hd] for j in range(lo, i + 1)])
             p = torch.softmax(s, 0)
             out[i, hd] = p @ v[lo:i + 1, kv]

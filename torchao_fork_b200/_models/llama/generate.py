@@ -221,9 +221,10 @@ def _load_model(checkpoint_path, device, precision):
 
 def _random_init_model(name, device, precision):
     """No checkpoints exist offline: the architecture `name` with seeded random weights (what bench.py measures)."""
-    from ..bitipel import Bitipel, bitipel_configs
-    if name in bitipel_configs:
-        return Bitipel.from_name(name, device, precision)
+    from ..registry import families
+    for fam in families().values():     # a family that lists the name among its configurations builds it itself
+        if fam.name != "llama" and fam.names is not None and name in fam.names():
+            return fam.from_name(name, device, precision)
     torch.manual_seed(1234)
     old = torch.get_default_dtype()
     torch.set_default_dtype(precision)

@@ -261,7 +261,7 @@ class Tadolix(nn.Module):
                 L.w_out = buf(q + "out", torch.cat([get(q + "left.o", (W, H * dv)), get(q + "right.o", (W, Rw))], 1))
                 L.z_b, L.x_b = buf(q + "right.z.b", get(q + "right.z.b", (Rw,))), buf(q + "right.x.b", get(q + "right.x.b", (Rw,)))
                 rel = get(q + "left.rel")
-                if rel.dim() != 2 or rel.shape[1] != H or rel.shape[0] < 2:
+                if rel.dim() != 2 or rel.shape[1] != H or rel.shape[0] < 1:
                     raise ValueError(f"{q}left.rel: shape {tuple(rel.shape)}, expected [buckets][{H}]")
                 L.dist_bias = buf(q + "left.dist_bias", distance_bias_table(w[q + "left.rel"].to(dev), a.bias_max, a.chunk))
             else:

@@ -144,14 +144,15 @@ class StepEngine:
             return self._logits(x, rows)
         # long portions: pieces of at most MAX_STEP_TOKENS tokens, in order (a piece may end inside a segment; the state
         # that a piece leaves is what the next one starts from, exactly as between steps)
-        out, rows_np = [], np.asarray(rows, np.int64)
+        rows_np = np.asarray(rows, np.int64)
+        result = torch.empty(len(rows), self.cfg.vocab_size, dtype=torch.float32, device=self.dev)
         for lo in range(0, total, MAX_STEP_TOKENS):
             hi = min(total, lo + MAX_STEP_TOKENS)
             x = self._run(tok[lo:hi], slot[lo:hi], pos[lo:hi])
-            sel = rows_np[(rows_np >= lo) & (rows_np < hi)] - lo
-            if len(sel):
-                out.append(self._logits(x, sel.tolist()))
-        return torch.cat(out) if out else torch.empty(0, self.cfg.vocab_size, device=self.dev)
+            where = np.flatnonzero((rows_np >= lo) & (rows_np < hi))     # wanted rows keep the order they were asked in
+            if len(where):
+                result[torch.from_numpy(where).to(self.dev)] = self._logits(x, (rows_np[where] - lo).tolist())
+        return result
 
     # ------------------------------------------------------------------------------------------------ pieces
     def _meta(self, slot: np.ndarray, pos: np.ndarray, tok: np.ndarray):
