@@ -190,7 +190,7 @@ AO_B200_API int ao_lm_rglru_scan(const float* gates, int64_t n, int block_width,
 /* Attention over chunks of `chunk` positions (a query sees the keys of its own chunk up to itself), H query heads over
  * G key/value heads.  ao_lm_qk_prep: unit-RMS queries (fp32 [n][H][d]) and keys (`dt` [n][G][d]) and the values in
  * `dt` [n][G][dv] from an fp32 projection row.  ao_lm_chunk_attention:
- *   score = softcap * tanh(scale * q.k / softcap) (softcap <= 0: none) + dist_bias[min(i - j, n_dist - 1)][head];
+ *   score = softcap * tanh(scale * q.k / softcap) (softcap <= 0: none) + dist_bias[head][min(i - j, n_dist - 1)];
  *   out[t][head * dv + c] = out_scale * softmax-weighted values * sigmoid(gate[t][head * dv + c]).
  * Keys of earlier steps come from the ring (ring_k [slots][chunk][G][d], ring_v likewise; position p in row p % chunk),
  * the step's own from kn / vn.  tile_first / tile_count: runs of <= tile_rows rows of one segment INSIDE one chunk
@@ -204,6 +204,17 @@ AO_B200_API int ao_lm_chunk_attention(const float* qn, const void* kn, const voi
                                       const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
                                       const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk,
                                       float scale, float softcap, float out_scale, void* out, int64_t ld_out, void* stream);
+/* The same attention on the tensor cores for prompt portions (bf16 storage; d and dv multiples of 16, dv <= 128): tiles
+ * of <= tile_rows (64) rows of one segment inside one chunk x one query head.  Queries and keys enter as bf16 operands
+ * with fp32 accumulation; the fp32 weights enter the value product as three bf16 parts, i.e. exactly.  The plan call
+ * gives tile_rows, or 0 when the shape is not covered (use ao_lm_chunk_attention then). */
+AO_B200_API int ao_lm_chunk_attention_prompt_plan(int dt, int H, int G, int d, int dv, int* tile_rows);
+AO_B200_API int ao_lm_chunk_attention_prompt(const float* qn, const void* kn, const void* vn, const void* ring_k,
+                                             const void* ring_v, int dt, const float* gate, int64_t ld_gate,
+                                             const float* dist_bias, int n_dist, const int32_t* slot, const int32_t* pos,
+                                             const int32_t* back, const int32_t* tile_first, const int32_t* tile_count,
+                                             int n_tiles, int H, int G, int d, int dv, int chunk, float scale, float softcap,
+                                             float out_scale, void* out, int64_t ld_out, void* stream);
 AO_B200_API int ao_lm_ring_append(const void* kn, const void* vn, int64_t n, int64_t k_row, int64_t v_row, int ring, int dt,
                                   const int32_t* slot, const int32_t* pos, const int32_t* ahead, void* ring_k, void* ring_v,
                                   void* stream);

@@ -268,8 +268,9 @@ def test_real_gated_recurrence_with_its_convolution_in_portions(tile, Rw, nb, ta
     assert torch.allclose(torch.cat(got), ref, rtol=2e-5, atol=2e-5)
 
 
-def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3):
-    """The three attention launches over `h` cut into portions, on a ring that starts full of stale rows."""
+def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3, tensor=False):
+    """The three attention launches over `h` cut into portions, on a ring that starts full of stale rows; `tensor`
+    picks the tensor-core form of the attention kernel."""
     lib, L = _lm()
     from torchao_fork_b200._models.tadolix.model import distance_bias_table
     from torchao_fork_b200._models.tadolix.step import chunk_tiles
@@ -282,8 +283,10 @@ def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3):
     ring_k = torch.full((slots, C, G, d), 3.0, dtype=dtype, device="cuda")
     ring_v = torch.full((slots, C, G, dv), -50.0, dtype=dtype, device="cuda")
     tr = __import__("ctypes").c_int()
-    lib.lm_check(L.ao_lm_chunk_attention_plan(dt, H, G, d, dv, __import__("ctypes").byref(tr)), "plan")
+    lib.lm_check((L.ao_lm_chunk_attention_prompt_plan if tensor else L.ao_lm_chunk_attention_plan)(
+        dt, H, G, d, dv, __import__("ctypes").byref(tr)), "plan")
     assert tr.value > 0
+    attend = L.ao_lm_chunk_attention_prompt if tensor else L.ao_lm_chunk_attention
     got, at = [], 0
     for c in cuts:
         pj = proj[at:at + c].contiguous().cuda()
@@ -295,10 +298,10 @@ def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3):
         f, k = chunk_tiles(np.array([0]), np.array([c]), np.arange(at, at + c), tr.value, C)
         tf, tc = _i32(f.tolist()), _i32(k.tolist())
         out = torch.zeros(c, H * dv + 2, dtype=dtype, device="cuda")
-        lib.lm_check(L.ao_lm_chunk_attention(qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), dt,
-                                             pj.data_ptr() + 4 * ((H + G) * d + G * dv), ld, bias.data_ptr(), C, sl.data_ptr(),
-                                             pos.data_ptr(), back.data_ptr(), tf.data_ptr(), tc.data_ptr(), len(f), H, G, d, dv, C,
-                                             a["scale"], a["softcap"], 0.5, out.data_ptr(), H * dv + 2, _st()), "chunk_attention")
+        lib.lm_check(attend(qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), dt,
+                            pj.data_ptr() + 4 * ((H + G) * d + G * dv), ld, bias.data_ptr(), C, sl.data_ptr(),
+                            pos.data_ptr(), back.data_ptr(), tf.data_ptr(), tc.data_ptr(), len(f), H, G, d, dv, C,
+                            a["scale"], a["softcap"], 0.5, out.data_ptr(), H * dv + 2, _st()), "chunk_attention")
         lib.lm_check(L.ao_lm_ring_append(kn.data_ptr(), vn.data_ptr(), c, G * d, G * dv, C, dt, sl.data_ptr(), pos.data_ptr(),
                                          ahead.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), _st()), "ring_append")
         assert float(out[:, H * dv:].abs().max()) == 0.0
@@ -314,6 +317,13 @@ ATTN_SHAPES = [dict(heads=6, kv_heads=2, dim=8, vdim=12, chunk=8, rows=6, bias_m
                dict(heads=3, kv_heads=3, dim=5, vdim=3, chunk=1, rows=2, bias_max=3),
                dict(heads=8, kv_heads=2, dim=64, vdim=64, chunk=64, rows=32, bias_max=128),
                dict(heads=2, kv_heads=1, dim=128, vdim=128, chunk=96, rows=8, bias_max=50)]
+
+
+def _forms(dtype, a):
+    """The forms of the attention kernel that cover a storage type and shape: fp32 arithmetic always, tensor cores for
+    bf16 with head sizes in multiples of 16."""
+    ok = dtype == torch.bfloat16 and a["dim"] % 16 == 0 and a["vdim"] % 16 == 0 and a["vdim"] <= 128
+    return [False, True] if ok else [False]
 
 
 @pytest.mark.parametrize("shape", range(len(ATTN_SHAPES)))
@@ -332,12 +342,13 @@ def test_chunk_attention_prompt_portions_decode_and_chunk_edges(shape, dtype):
     cuts = [max(1, C // 2), 1, 1]
     rest = T - sum(cuts)
     cuts += [rest - 4, 2, 1, 1]
-    got = _attention_alone(a, w, h, cuts, dtype)
     tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
-    assert torch.allclose(got, ref, **tol)
-    whole = _attention_alone(a, w, h, [T], dtype)
-    assert torch.allclose(whole, ref, **tol)
-    assert torch.allclose(whole, got, **(dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else tol))
+    for tensor in _forms(dtype, a):
+        got = _attention_alone(a, w, h, cuts, dtype, tensor=tensor)
+        assert torch.allclose(got, ref, **tol), tensor
+        whole = _attention_alone(a, w, h, [T], dtype, tensor=tensor)
+        assert torch.allclose(whole, ref, **tol), tensor
+        assert torch.allclose(whole, got, **(dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else tol)), tensor
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -346,13 +357,13 @@ def test_chunk_attention_one_dominant_key_inside_and_outside_the_chunk(dtype, ke
     """One key is made to match one query far better than every other key, and its value stands out.  Inside the
     query's chunk it must take nearly all the weight, in the chunk before it must not be seen at all — from a prompt
     row and from a row decoded alone."""
-    kw = dict(heads=2, kv_heads=1, dim=16, vdim=8, chunk=16, rows=8, bias_max=16, scale=3.0, softcap=200.0)
+    kw = dict(heads=2, kv_heads=1, dim=16, vdim=16, chunk=16, rows=8, bias_max=16, scale=3.0, softcap=200.0)
     cfg = O.make_config([O.attention_layer(**kw)], width=32)
     a = cfg["layers"][0]["mixer"]["left"]
     w = {k: v.double() for k, v in O.random_weights(cfg, 13).items()}
     p = "l0.mix.left."
     eye = torch.cat([torch.eye(16, dtype=F64), torch.zeros(16, 16, dtype=F64)], 1)      # queries and keys read the first half
-    w[p + "o"] = torch.eye(16, dtype=F64)
+    w[p + "o"] = torch.eye(32, dtype=F64)
     w[p + "q"], w[p + "k"] = torch.cat([eye, eye]), eye
     w[p + "v"][:, :16] = 0.0                                                           # values read the second half
     w[p + "rel"] = torch.zeros_like(w[p + "rel"])
@@ -365,13 +376,14 @@ def test_chunk_attention_one_dominant_key_inside_and_outside_the_chunk(dtype, ke
     same_chunk = key // 16 == query // 16 and key <= query
     # gate 1/2, branch scale 1/2: the far key shares the weight with the query's own key, or is not there at all
     expect = 0.25 * (0.5 * (v_key + v_own) if same_chunk else v_own)
-    assert torch.allclose(ref[query, :8], expect, rtol=0, atol=1e-3)
+    assert torch.allclose(ref[query, :16], expect, rtol=0, atol=1e-3)
     tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
     for cuts in ([T], [query, 1, T - query - 1], [key + 1, T - key - 1] if key + 1 < T else [T]):
         cuts = [c for c in cuts if c > 0]
-        got = _attention_alone(a, w, h, cuts, dtype)
-        assert torch.allclose(got[query], ref[query], **tol), cuts
-        assert torch.allclose(got, ref, **tol), cuts
+        for tensor in _forms(dtype, a):
+            got = _attention_alone(a, w, h, cuts, dtype, tensor=tensor)
+            assert torch.allclose(got[query], ref[query], **tol), (cuts, tensor)
+            assert torch.allclose(got, ref, **tol), (cuts, tensor)
 
 
 def test_gelu_gated_product():
@@ -448,6 +460,31 @@ def test_prefill_equals_token_by_token_and_portions(dtype, name):
             at += c
         st.release("r")
         assert _err(torch.cat(got), ref) <= tol, cuts
+
+
+@pytest.mark.parametrize("min_rows", [1, 10 ** 9])
+def test_either_attention_form_for_every_portion_and_batch(monkeypatch, min_rows):
+    """The switch between the two forms of the attention kernel is a matter of speed: with the tensor-core form forced
+    for every step (single decoded tokens included), and with it switched off, the logits stay the oracle's."""
+    from torchao_fork_b200._models.tadolix import step as S
+    monkeypatch.setattr(S, "PROMPT_MIN_ROWS", min_rows)
+    cfg = _tensor()
+    w = O.random_weights(cfg, 29)
+    ta, tb = _tokens(cfg, 75, 9), _tokens(cfg, 40, 10)
+    ra, rb = O.forward(cfg, w, ta), O.forward(cfg, w, tb)
+    tol = max(_bf16_tol(cfg, w, ta), _bf16_tol(cfg, w, tb))
+    m = _model(cfg, w, torch.bfloat16)
+    eng, st = m.step_engine, m.states
+    ga = [eng.step([(st.slot_of("a"), ta[:33])], "all")]
+    both = eng.step([(st.slot_of("a"), ta[33:70]), (st.slot_of("b"), tb[:38])], "all")
+    ga.append(both[:37])
+    gb = [both[37:]]
+    for i in range(2):
+        both = eng.step([(st.slot_of("b"), tb[38 + i:39 + i]), (st.slot_of("a"), ta[70 + i:71 + i])], "all")
+        gb.append(both[:1])
+        ga.append(both[1:])
+    ga.append(eng.step([(st.slot_of("a"), ta[72:])], "all"))
+    assert _err(torch.cat(ga), ra) <= tol and _err(torch.cat(gb), rb) <= tol
 
 
 def test_scan_tiles_and_pieces_cut_inside_a_step(monkeypatch):

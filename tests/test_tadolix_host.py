@@ -61,11 +61,11 @@ def test_distance_bias_table_is_the_bucket_function(B, D):
     rel = torch.arange(B * 3, dtype=torch.float32).view(B, 3)
     n = 3 * D
     tab = distance_bias_table(rel, D, n)
-    assert tab.shape == (n, 3)
+    assert tab.shape == (3, n)
     for dist in range(n):
-        assert torch.equal(tab[dist], rel[O.distance_bucket(dist, B, D)]), dist
+        assert torch.equal(tab[:, dist], rel[O.distance_bucket(dist, B, D)]), dist
     # one row per distance below B // 2, the last row from bias_max on, never decreasing in between
-    rows = (tab[:, 0] / 3).long().tolist()
+    rows = (tab[0] / 3).long().tolist()
     assert rows[: B // 2] == list(range(B // 2)) and rows[D] == B - 1 and rows == sorted(rows)
 
 

@@ -166,6 +166,9 @@ LM_SIGNATURES = {
     "ao_lm_chunk_attention_plan": [_i32, _i32, _i32, _i32, _i32, _p32],
     "ao_lm_chunk_attention": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                               _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
+    "ao_lm_chunk_attention_prompt_plan": [_i32, _i32, _i32, _i32, _i32, _p32],
+    "ao_lm_chunk_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                     _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
     "ao_lm_ring_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _LM_RESTYPES = {"ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64}

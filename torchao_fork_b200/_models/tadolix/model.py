@@ -150,7 +150,7 @@ class TadolixArgs:
 
 
 def distance_bias_table(rel: torch.Tensor, bias_max: int, n_dist: int) -> torch.Tensor:
-    """rel [B][H] (one row per bucket) -> fp32 [n_dist][H], row n = the bias at distance n: one bucket per distance
+    """rel [B][H] (one row per bucket) -> fp32 [H][n_dist], column n = the bias at distance n: one bucket per distance
     below B // 2, then (B - B // 2) logarithmic steps up to bias_max, everything farther in the last bucket."""
     B = rel.shape[0]
     half = B // 2
@@ -162,7 +162,7 @@ def distance_bias_table(rel: torch.Tensor, bias_max: int, n_dist: int) -> torch.
             rows.append(B - 1)
         else:
             rows.append(min(B - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half) * (B - half)))))
-    return rel.to(torch.float32)[torch.tensor(rows, dtype=torch.long, device=rel.device)].contiguous()
+    return rel.to(torch.float32)[torch.tensor(rows, dtype=torch.long, device=rel.device)].t().contiguous()
 
 
 def _pattern(n_layer, width, heads, kv_heads, dim, chunk, ff, vocab, streams=4, taps=4, blocks=None):

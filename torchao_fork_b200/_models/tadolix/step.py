@@ -29,6 +29,10 @@ from .model import RGLRU_DECAY, Tadolix
 MAX_STEP_TOKENS = 4096
 # rows of a recurrence tile; a step whose segments all fit one tile scans in one launch
 SCAN_TILE = 64
+# steps that bring at least this many rows per sequence (on average) attend with the tensor-core kernel (bf16 models,
+# head sizes it covers); decoded tokens and short portions use the fp32 kernel, which shares a key block between the
+# few rows of a tile and all query heads of a key/value head
+PROMPT_MIN_ROWS = 16
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -44,7 +48,7 @@ class StepMeta:
     back: torch.Tensor
     ahead: torch.Tensor
     scan: tuple          # (tile_first, tile_count, n_tiles, seg_tile0 | None, seg_tiles | None, n_segments)
-    attn: Dict[tuple, tuple]   # (tile_rows, chunk) -> (tile_first, tile_count, n_tiles)
+    attn: Dict[tuple, tuple]   # attention shape -> (tile_first, tile_count, n_tiles, tensor-core form?)
 
 
 def segments_of(slot: np.ndarray, pos: np.ndarray):
@@ -100,7 +104,7 @@ class StepEngine:
             torch.set_float32_matmul_precision("highest")
         self.launches = 0
         # rows of one sequence that an attention CTA takes, per attention shape of the model
-        self.attn_keys = {}
+        self.attn_keys, self.prompt_keys = {}, {}
         for la in self.cfg.layers:
             if la.type != "parallel":
                 continue
@@ -110,7 +114,11 @@ class StepEngine:
                           "chunk_attention_plan")
             if tr.value <= 0:
                 raise NotImplementedError(f"attention shape not covered by the kernels: {a}")
-            self.attn_keys[(a.heads, a.kv_heads, a.dim, a.vdim, a.chunk)] = (tr.value, a.chunk)
+            self.attn_keys[(a.heads, a.kv_heads, a.dim, a.vdim, a.chunk)] = (tr.value, a.chunk, False)
+            _lib.lm_check(self.L.ao_lm_chunk_attention_prompt_plan(self.dt, a.heads, a.kv_heads, a.dim, a.vdim, ctypes.byref(tr)),
+                          "chunk_attention_prompt_plan")
+            if tr.value > 0:
+                self.prompt_keys[(a.heads, a.kv_heads, a.dim, a.vdim, a.chunk)] = (tr.value, a.chunk, True)
 
     # ------------------------------------------------------------------------------------------------ public
     @torch.no_grad()
@@ -168,8 +176,11 @@ class StepEngine:
         if seg0 is not None:
             parts += [seg0, segn]
         attn_np = {}
-        for key in sorted(set(self.attn_keys.values())):
-            attn_np[key] = chunk_tiles(starts, counts, pos, *key)
+        prompt = n >= PROMPT_MIN_ROWS * len(starts)
+        meta_shapes = {shape: (self.prompt_keys[shape] if prompt and shape in self.prompt_keys else key)
+                       for shape, key in self.attn_keys.items()}
+        for key in sorted(set(meta_shapes.values())):
+            attn_np[key] = chunk_tiles(starts, counts, pos, key[0], key[1])
             parts += list(attn_np[key])
         packed = torch.from_numpy(np.concatenate(parts)).to(self.dev, non_blocking=True)
         o = [0]
@@ -189,10 +200,11 @@ class StepEngine:
             meta.scan = (tf, tc, nt, take(len(seg0)), take(len(seg0)), len(seg0))
         else:
             meta.scan = (tf, tc, nt, None, None, 0)
-        meta.attn = {}
+        tables = {}
         for key in sorted(attn_np):
             k = len(attn_np[key][0])
-            meta.attn[key] = (take(k), take(k), k)
+            tables[key] = (take(k), take(k), k, key[2])
+        meta.attn = {shape: tables[key] for shape, key in meta_shapes.items()}
         return d_tok, meta
 
     def _run(self, tok: np.ndarray, slot: np.ndarray, pos: np.ndarray) -> torch.Tensor:
@@ -280,10 +292,10 @@ class StepEngine:
         both = torch.empty(n, H * dv + Rw, dtype=tdt, device=dev)          # [attention result | recurrence result]
         _lib.lm_check(L.ao_lm_qk_prep(_p(proj), lay.ld, lay.q_off, lay.k_off, lay.v_off, n, H, G, d, dv, self.cfg.norm_eps, dt,
                                       _p(qn), _p(kn), _p(vn), st), "qk_prep")
-        tf, tc, nt = meta.attn[self.attn_keys[(H, G, d, dv, a.chunk)]]
-        _lib.lm_check(L.ao_lm_chunk_attention(
+        tf, tc, nt, tensor = meta.attn[(H, G, d, dv, a.chunk)]
+        _lib.lm_check((L.ao_lm_chunk_attention_prompt if tensor else L.ao_lm_chunk_attention)(
             _p(qn), _p(kn), _p(vn), _p(rs.ring.k), _p(rs.ring.v), dt, proj.data_ptr() + 4 * lay.g_off, lay.ld, _p(lay.dist_bias),
-            lay.dist_bias.shape[0], _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, H, G, d, dv, a.chunk,
+            lay.dist_bias.shape[1], _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, H, G, d, dv, a.chunk,
             a.scale, a.softcap, mx.left_scale, _p(both), both.shape[1], st), "chunk_attention")
         _lib.lm_check(L.ao_lm_ring_append(_p(kn), _p(vn), n, G * d, G * dv, a.chunk, dt, _p(meta.slot), _p(meta.pos),
                                           _p(meta.ahead), _p(rs.ring.k), _p(rs.ring.v), st), "ring_append")
@@ -374,7 +386,7 @@ class GraphDecodeEngine:
         meta.n = B
         meta.slot, meta.pos, meta.back, meta.ahead = ar, torch.zeros(B, dtype=torch.int32, device=dev), zeros, zeros
         meta.scan = (ar, ones, B, None, None, 0)       # one row per sequence: every tile is a whole segment
-        meta.attn = {key: (ar, ones, B) for key in set(self.eng.attn_keys.values())}
+        meta.attn = {shape: (ar, ones, B, False) for shape in self.eng.attn_keys}
         self.meta, self.pos, self.rows = meta, meta.pos, ar
         self.graph = None
         self.graph_stream = None

@@ -61,7 +61,7 @@ struct ChunkArgs {
   const void *ring_k, *ring_v;
   const float* gate;         // pre-activation, row stride ld_gate, H * dv per row
   int64_t ld_gate;
-  const float* bias;         // [n_dist][H]
+  const float* bias;         // [H][n_dist]
   int n_dist;
   const int32_t *slot, *pos, *back, *tile_first, *tile_count;
   int H, G, d, dv, C;
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
       if (kk <= lim) {
         sc *= a.scale;
         if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
-        sc += a.bias[(int64_t)min(lim - kk, a.n_dist - 1) * a.H + qh];
+        sc += a.bias[(int64_t)qh * a.n_dist + min(lim - kk, a.n_dist - 1)];
       } else {
         sc = -INFINITY;
       }
