@@ -24,6 +24,8 @@ extern "C" {
 enum { AO_LM_BF16 = 0, AO_LM_F32 = 1 };
 
 AO_B200_API int ao_lm_abi_version(void);
+/* text of the CUDA error behind the last AO_B200_ERR_CUDA that a call of this library returned ("" if none) */
+AO_B200_API const char* ao_lm_last_cuda_error(void);
 
 /* x[t][:] = table[tok[t]][:]  (fp32 out) */
 AO_B200_API int ao_lm_embed(const void* table, int dt, const int64_t* tok, int64_t n, int64_t width, float* x, void* stream);
@@ -199,11 +201,15 @@ AO_B200_API int ao_lm_rglru_scan(const float* gates, int64_t n, int block_width,
 AO_B200_API int ao_lm_qk_prep(const float* proj, int64_t ld, int64_t q_off, int64_t k_off, int64_t v_off, int64_t n, int H, int G,
                               int d, int dv, float eps, int dt, float* qn, void* kn, void* vn, void* stream);
 AO_B200_API int ao_lm_chunk_attention_plan(int dt, int H, int G, int d, int dv, int* tile_rows);
+/* 1 < n_split <= 64 spreads a tile's key blocks over that many CTAs and adds a merge launch (few rows over many keys:
+ * a decoded token late in its chunk); shares past a sequence's keys leave at once, so n_split may be fixed for a graph. */
+AO_B200_API int64_t ao_lm_chunk_attention_workspace_bytes(int n_tiles, int G, int dv, int n_split);
 AO_B200_API int ao_lm_chunk_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
                                       int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
                                       const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
                                       const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk,
-                                      float scale, float softcap, float out_scale, void* out, int64_t ld_out, void* stream);
+                                      float scale, float softcap, float out_scale, int n_split, void* workspace,
+                                      int64_t workspace_bytes, void* out, int64_t ld_out, void* stream);
 /* The same attention on the tensor cores for prompt portions (bf16 storage; d and dv multiples of 16, dv <= 128): tiles
  * of <= tile_rows (64) rows of one segment inside one chunk x one query head.  Queries and keys enter as bf16 operands
  * with fp32 accumulation; the fp32 weights enter the value product as three bf16 parts, i.e. exactly.  The plan call

@@ -268,7 +268,7 @@ def test_real_gated_recurrence_with_its_convolution_in_portions(tile, Rw, nb, ta
     assert torch.allclose(torch.cat(got), ref, rtol=2e-5, atol=2e-5)
 
 
-def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3, tensor=False):
+def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3, tensor=False, n_split=1):
     """The three attention launches over `h` cut into portions, on a ring that starts full of stale rows; `tensor`
     picks the tensor-core form of the attention kernel."""
     lib, L = _lm()
@@ -298,10 +298,14 @@ def _attention_alone(a, w, h, cuts, dtype, slot=1, slots=3, tensor=False):
         f, k = chunk_tiles(np.array([0]), np.array([c]), np.arange(at, at + c), tr.value, C)
         tf, tc = _i32(f.tolist()), _i32(k.tolist())
         out = torch.zeros(c, H * dv + 2, dtype=dtype, device="cuda")
-        lib.lm_check(attend(qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), dt,
-                            pj.data_ptr() + 4 * ((H + G) * d + G * dv), ld, bias.data_ptr(), C, sl.data_ptr(),
-                            pos.data_ptr(), back.data_ptr(), tf.data_ptr(), tc.data_ptr(), len(f), H, G, d, dv, C,
-                            a["scale"], a["softcap"], 0.5, out.data_ptr(), H * dv + 2, _st()), "chunk_attention")
+        args = (qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), dt,
+                pj.data_ptr() + 4 * ((H + G) * d + G * dv), ld, bias.data_ptr(), C, sl.data_ptr(), pos.data_ptr(), back.data_ptr(),
+                tf.data_ptr(), tc.data_ptr(), len(f), H, G, d, dv, C, a["scale"], a["softcap"], 0.5)
+        if tensor:
+            lib.lm_check(attend(*args, out.data_ptr(), H * dv + 2, _st()), "chunk_attention_prompt")
+        else:
+            ws = torch.empty(max(16, int(L.ao_lm_chunk_attention_workspace_bytes(len(f), G, dv, n_split))), dtype=torch.uint8, device="cuda")
+            lib.lm_check(attend(*args, n_split, ws.data_ptr(), ws.numel(), out.data_ptr(), H * dv + 2, _st()), "chunk_attention")
         lib.lm_check(L.ao_lm_ring_append(kn.data_ptr(), vn.data_ptr(), c, G * d, G * dv, C, dt, sl.data_ptr(), pos.data_ptr(),
                                          ahead.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), _st()), "ring_append")
         assert float(out[:, H * dv:].abs().max()) == 0.0
@@ -349,6 +353,10 @@ def test_chunk_attention_prompt_portions_decode_and_chunk_edges(shape, dtype):
         whole = _attention_alone(a, w, h, [T], dtype, tensor=tensor)
         assert torch.allclose(whole, ref, **tol), tensor
         assert torch.allclose(whole, got, **(dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else tol)), tensor
+    # the keys of a tile spread over several CTAs (more shares than key blocks included) and merged
+    for n_split in (2, 5):
+        got = _attention_alone(a, w, h, cuts, dtype, n_split=n_split)
+        assert torch.allclose(got, ref, **tol), n_split
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -130,6 +130,7 @@ _p32 = ctypes.POINTER(ctypes.c_int)
 
 LM_SIGNATURES = {
     "ao_lm_abi_version": [],
+    "ao_lm_last_cuda_error": [],
     "ao_lm_embed": [_vp, _i32, _vp, _i64, _i64, _vp, _vp],
     "ao_lm_token_shift": [_vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _vp, _vp],
     "ao_lm_residual_norm": [_vp, _vp, _i32, _vp, _i32, _f32, _f32, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _vp, _vp],
@@ -164,14 +165,16 @@ LM_SIGNATURES = {
                          _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp],
     "ao_lm_qk_prep": [_vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp],
     "ao_lm_chunk_attention_plan": [_i32, _i32, _i32, _i32, _i32, _p32],
+    "ao_lm_chunk_attention_workspace_bytes": [_i32, _i32, _i32, _i32],
     "ao_lm_chunk_attention": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
-                              _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
+                              _i32, _i32, _i32, _f32, _f32, _f32, _i32, _vp, _i64, _vp, _i64, _vp],
     "ao_lm_chunk_attention_prompt_plan": [_i32, _i32, _i32, _i32, _i32, _p32],
     "ao_lm_chunk_attention_prompt": [_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _f32, _f32, _vp, _i64, _vp],
     "ao_lm_ring_append": [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
 }
-_LM_RESTYPES = {"ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64}
+_LM_RESTYPES = {"ao_lm_last_cuda_error": ctypes.c_char_p, "ao_lm_latent_attention_workspace_bytes": _i64, "ao_lm_scan_workspace_bytes": _i64,
+                "ao_lm_chunk_attention_workspace_bytes": _i64}
 _lm = None
 _LM_ERRORS = {1: "invalid argument", 2: "unsupported shape", 3: "CUDA launch failed", 4: "workspace too small"}
 
@@ -193,4 +196,5 @@ def lm():
 
 def lm_check(code, what):
     if code != 0:
-        raise RuntimeError(f"libao_b200_lm: {what} failed: {_LM_ERRORS.get(code, 'error')} (code {code})")
+        why = f": {lm().ao_lm_last_cuda_error().decode()}" if code == 3 else ""
+        raise RuntimeError(f"libao_b200_lm: {what} failed: {_LM_ERRORS.get(code, 'error')}{why} (code {code})")

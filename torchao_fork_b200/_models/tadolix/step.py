@@ -28,7 +28,7 @@ from .model import RGLRU_DECAY, Tadolix
 # a portion longer than this is cut into pieces (bounds the workspace)
 MAX_STEP_TOKENS = 4096
 # rows of a recurrence tile; a step whose segments all fit one tile scans in one launch
-SCAN_TILE = 64
+SCAN_TILE = 32
 # steps that bring at least this many rows per sequence (on average) attend with the tensor-core kernel (bf16 models,
 # head sizes it covers); decoded tokens and short portions use the fp32 kernel, which shares a key block between the
 # few rows of a tile and all query heads of a key/value head
@@ -103,6 +103,7 @@ class StepEngine:
             torch.backends.cudnn.allow_tf32 = False
             torch.set_float32_matmul_precision("highest")
         self.launches = 0
+        self.sm_count = torch.cuda.get_device_properties(self.dev).multi_processor_count
         # rows of one sequence that an attention CTA takes, per attention shape of the model
         self.attn_keys, self.prompt_keys = {}, {}
         for la in self.cfg.layers:
@@ -273,6 +274,14 @@ class StepEngine:
             return torch.mm(a, w.t(), out_dtype=torch.float32)
         return torch.mm(a, w.t())
 
+    def _splits(self, ctas: int, chunk: int) -> int:
+        """Key splits of the fp32 attention kernel: enough CTAs to fill the GPU when few rows attend over a long chunk
+        (a decoded token late in its chunk).  It depends on sizes only, so a captured graph keeps it."""
+        key_blocks = -(-chunk // 32)
+        if ctas >= self.sm_count or key_blocks <= 2:
+            return 1
+        return max(1, min(key_blocks, -(-2 * self.sm_count // ctas), 64))
+
     def _scan_ws(self, meta: StepMeta, channels: int):
         tf, tc, nt, seg0, segn, ns = meta.scan
         if seg0 is None:
@@ -293,10 +302,18 @@ class StepEngine:
         _lib.lm_check(L.ao_lm_qk_prep(_p(proj), lay.ld, lay.q_off, lay.k_off, lay.v_off, n, H, G, d, dv, self.cfg.norm_eps, dt,
                                       _p(qn), _p(kn), _p(vn), st), "qk_prep")
         tf, tc, nt, tensor = meta.attn[(H, G, d, dv, a.chunk)]
-        _lib.lm_check((L.ao_lm_chunk_attention_prompt if tensor else L.ao_lm_chunk_attention)(
-            _p(qn), _p(kn), _p(vn), _p(rs.ring.k), _p(rs.ring.v), dt, proj.data_ptr() + 4 * lay.g_off, lay.ld, _p(lay.dist_bias),
-            lay.dist_bias.shape[1], _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, H, G, d, dv, a.chunk,
-            a.scale, a.softcap, mx.left_scale, _p(both), both.shape[1], st), "chunk_attention")
+        common = (_p(qn), _p(kn), _p(vn), _p(rs.ring.k), _p(rs.ring.v), dt, proj.data_ptr() + 4 * lay.g_off, lay.ld,
+                  _p(lay.dist_bias), lay.dist_bias.shape[1], _p(meta.slot), _p(meta.pos), _p(meta.back), _p(tf), _p(tc), nt, H, G, d,
+                  dv, a.chunk, a.scale, a.softcap, mx.left_scale)
+        split = 0
+        if tensor:
+            _lib.lm_check(L.ao_lm_chunk_attention_prompt(*common, _p(both), both.shape[1], st), "chunk_attention_prompt")
+        else:
+            ns = self._splits(nt * G, a.chunk)
+            nbytes = int(L.ao_lm_chunk_attention_workspace_bytes(nt, G, dv, ns))
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+            _lib.lm_check(L.ao_lm_chunk_attention(*common, ns, _p(ws), ws.numel(), _p(both), both.shape[1], st), "chunk_attention")
+            split = 1 if ns > 1 else 0
         _lib.lm_check(L.ao_lm_ring_append(_p(kn), _p(vn), n, G * d, G * dv, a.chunk, dt, _p(meta.slot), _p(meta.pos),
                                           _p(meta.ahead), _p(rs.ring.k), _p(rs.ring.v), st), "ring_append")
         sf, sc, snt, seg0, segn, ns = meta.scan
@@ -306,7 +323,7 @@ class StepEngine:
             _p(meta.pos), _p(meta.back), _p(sf), _p(sc), snt, _p(seg0), _p(segn), ns, _p(ws), mx.right_scale,
             both.data_ptr() + H * dv * both.element_size(), both.shape[1], st), "mingru_scan")
         y = self._mm_f32(both, lay.w_out)
-        return y, 6 + (2 if seg0 is not None else 0)
+        return y, 6 + split + (2 if seg0 is not None else 0)
 
     def _rglru(self, lay, mx, rs, h, meta: StepMeta, st):
         """gelu branch x real-gated linear recurrence over a short convolution -> (fp32 [n][W], launches)."""

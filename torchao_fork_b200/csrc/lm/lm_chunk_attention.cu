@@ -68,6 +68,8 @@ struct ChunkArgs {
   float scale, softcap, out_scale;
   void* out;                 // [n][ld_out], H * dv per row
   int64_t ld_out;
+  int n_split;               // > 1: blockIdx.z takes a share of the key blocks and leaves (max, denominator, sums) in ws
+  float* ws;                 // [tiles][G][n_split][kWarps * kPairSlots][dv + 2]
 };
 
 // One CTA = a tile of consecutive rows of one sequence inside one chunk x one key/value head; a warp owns up to
@@ -106,7 +108,10 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
 #pragma unroll
     for (int e = 0; e < kMaxDvLane; ++e) o[s][e] = 0.f;
   }
-  for (int k0 = 0; k0 < nk; k0 += kKeys) {
+  // this CTA's share of the key blocks
+  const int blocks = (nk + kKeys - 1) / kKeys, per = (blocks + a.n_split - 1) / a.n_split;
+  const int k_lo = (int)blockIdx.z * per * kKeys, k_end = min(nk, ((int)blockIdx.z + 1) * per * kKeys);
+  for (int k0 = k_lo; k0 < k_end; k0 += kKeys) {
     __syncthreads();   // the previous block is used up (and, the first time, the queries are in place)
     for (int i = threadIdx.x; i < kKeys * d; i += blockDim.x) {
       const int j = i / d, c = i - j * d, kk = k0 + j;
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
         sc = -INFINITY;
       }
       const float top = fmaxf(mx[s], warp_max(sc));   // key k0 <= lim is visible: top is finite
-      const float corr = expf(mx[s] - top);           // 0 the first time
+      const float corr = mx[s] == -INFINITY ? 0.f : expf(mx[s] - top);
       const float p = expf(sc - top);
       mx[s] = top;
       den[s] = den[s] * corr + warp_sum(p);
@@ -160,6 +165,22 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
       __syncwarp();
     }
   }
+  if (a.n_split > 1) {
+    // partial results of this share; a share without visible keys leaves max = -inf, denominator 0
+#pragma unroll
+    for (int s = 0; s < kPairSlots; ++s) {
+      const int pr = warp + s * kWarps;
+      if (pr >= npairs) continue;
+      float* w = a.ws + ((((int64_t)tile * a.G + g) * a.n_split + blockIdx.z) * (kWarps * kPairSlots) + pr) * (dv + 2);
+      if (lane == 0) w[0] = mx[s], w[1] = den[s];
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) {
+        const int c = lane + 32 * e;
+        if (c < dv) w[2 + c] = o[s][e];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int s = 0; s < kPairSlots; ++s) {
     const int pr = warp + s * kWarps;
@@ -173,6 +194,44 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_kernel(ChunkArgs 
     for (int e = 0; e < kMaxDvLane; ++e) {
       const int c = lane + 32 * e;
       if (c < dv) stf(dst + c, o[s][e] * inv / (1.f + expf(-gt[c])));
+    }
+  }
+}
+
+// the shares of one (tile, key/value head) put together: one warp per (row, query head) pair
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32) chunk_attention_merge_kernel(ChunkArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, g = blockIdx.y, dv = a.dv, rep = a.H / a.G;
+  const int first = a.tile_first[tile], npairs = a.tile_count[tile] * rep;
+  for (int pr = warp; pr < npairs; pr += kWarps) {
+    const float* w0 = a.ws + ((((int64_t)tile * a.G + g) * a.n_split) * (kWarps * kPairSlots) + pr) * (dv + 2);
+    const int64_t stride = (int64_t)(kWarps * kPairSlots) * (dv + 2);
+    float top = -INFINITY;
+    for (int z = 0; z < a.n_split; ++z) top = fmaxf(top, w0[z * stride]);
+    float den = 0.f, o[kMaxDvLane];
+#pragma unroll
+    for (int e = 0; e < kMaxDvLane; ++e) o[e] = 0.f;
+    for (int z = 0; z < a.n_split; ++z) {
+      const float* w = w0 + z * stride;
+      if (w[0] == -INFINITY) continue;
+      const float f = expf(w[0] - top);
+      den = fmaf(w[1], f, den);
+#pragma unroll
+      for (int e = 0; e < kMaxDvLane; ++e) {
+        const int c = lane + 32 * e;
+        if (c < dv) o[e] = fmaf(w[2 + c], f, o[e]);
+      }
+    }
+    const int r = pr / rep, qh = g * rep + pr % rep;
+    const int64_t t = first + r;
+    const float inv = a.out_scale / den;
+    const float* gt = a.gate + t * a.ld_gate + (int64_t)qh * dv;
+    T* dst = static_cast<T*>(a.out) + t * a.ld_out + (int64_t)qh * dv;
+#pragma unroll
+    for (int e = 0; e < kMaxDvLane; ++e) {
+      const int c = lane + 32 * e;
+      if (c < dv) stf(dst + c, o[e] * inv / (1.f + expf(-gt[c])));
     }
   }
 }
@@ -215,18 +274,27 @@ extern "C" int ao_lm_chunk_attention_plan(int dt, int H, int G, int d, int dv, i
   return AO_B200_OK;
 }
 
+extern "C" int64_t ao_lm_chunk_attention_workspace_bytes(int n_tiles, int G, int dv, int n_split) {
+  return n_split > 1 ? (int64_t)n_tiles * G * n_split * (kWarps * kPairSlots) * (dv + 2) * 4 : 0;
+}
+
 extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void* vn, const void* ring_k, const void* ring_v,
                                      int dt, const float* gate, int64_t ld_gate, const float* dist_bias, int n_dist,
                                      const int32_t* slot, const int32_t* pos, const int32_t* back, const int32_t* tile_first,
                                      const int32_t* tile_count, int n_tiles, int H, int G, int d, int dv, int chunk, float scale,
-                                     float softcap, float out_scale, void* out, int64_t ld_out, void* stream) {
+                                     float softcap, float out_scale, int n_split, void* workspace, int64_t workspace_bytes,
+                                     void* out, int64_t ld_out, void* stream) {
   LM_CHECK_ARG(qn && kn && vn && ring_k && ring_v && gate && dist_bias && slot && pos && back && tile_first && tile_count && out);
-  LM_CHECK_ARG(n_tiles > 0 && n_dist > 0 && chunk > 0 && G > 0 && G <= 65535);
+  LM_CHECK_ARG(n_tiles > 0 && n_dist > 0 && chunk > 0 && G > 0 && G <= 65535 && n_split >= 1 && n_split <= 64);
+  if (n_split > 1) {
+    LM_CHECK_ARG(workspace);
+    if (workspace_bytes < ao_lm_chunk_attention_workspace_bytes(n_tiles, G, dv, n_split)) return AO_B200_ERR_WORKSPACE;
+  }
   if (generic_tile_rows(H, G) == 0 || dv > 32 * kMaxDvLane) return AO_B200_ERR_UNSUPPORTED;
   const size_t smem = generic_smem(d, dv);
   if (smem > 200 * 1024) return AO_B200_ERR_UNSUPPORTED;
   ChunkArgs a{qn, kn, vn, ring_k, ring_v, gate, ld_gate, dist_bias, n_dist, slot, pos, back, tile_first, tile_count,
-              H, G, d, dv, chunk, scale, softcap, out_scale, out, ld_out};
+              H, G, d, dv, chunk, scale, softcap, out_scale, out, ld_out, n_split, static_cast<float*>(workspace)};
   LM_DISPATCH(dt, {
     auto kern = chunk_attention_kernel<T>;
     if (smem > 48 * 1024) {
@@ -236,7 +304,9 @@ extern "C" int ao_lm_chunk_attention(const float* qn, const void* kn, const void
         set = true;
       }
     }
-    kern<<<dim3((unsigned)n_tiles, (unsigned)G), kWarps * 32, smem, lm_stream(stream)>>>(a);
+    kern<<<dim3((unsigned)n_tiles, (unsigned)G, (unsigned)n_split), kWarps * 32, smem, lm_stream(stream)>>>(a);
+    if (n_split > 1)
+      chunk_attention_merge_kernel<T><<<dim3((unsigned)n_tiles, (unsigned)G), kWarps * 32, 0, lm_stream(stream)>>>(a);
   });
   return lm_launch_status();
 }

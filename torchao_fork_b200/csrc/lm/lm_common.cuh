@@ -26,7 +26,14 @@
     }                                     \
   } while (0)
 
-static inline int lm_launch_status() { return cudaGetLastError() == cudaSuccess ? AO_B200_OK : AO_B200_ERR_CUDA; }
+// the CUDA error behind the last AO_B200_ERR_CUDA that this library returned (0 = none); ao_lm_last_cuda_error reads it
+extern int g_lm_last_cuda_error;
+static inline int lm_launch_status() {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return AO_B200_OK;
+  g_lm_last_cuda_error = (int)e;
+  return AO_B200_ERR_CUDA;
+}
 static inline cudaStream_t lm_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
 namespace lm {

@@ -19,27 +19,48 @@ constexpr int kScanThreads = 128;
 // y[t][c] = (residual ? v(t) : 0) + out_bias[c] + sum_j kern[c][j] * v(t - (taps - 1 - j)),  v(row) = x[row][c] + in_bias[c];
 // rows in front of the step come from state[slot][k][c] (k-th oldest of the taps - 1 kept inputs, bias included), rows
 // in front of position 0 are zero.
+constexpr int kConvRows = 8;   // rows of one CTA: taps, metadata and the rows' inputs are loaded once, all up front
 template <typename T>
-__global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const T* __restrict__ in_bias, int64_t C, int taps,
-                                   const T* __restrict__ kern, const T* __restrict__ out_bias, int residual,
+__global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, const T* __restrict__ in_bias, int64_t n, int64_t C,
+                                   int taps, const T* __restrict__ kern, const T* __restrict__ out_bias, int residual,
                                    const float* __restrict__ state, const int32_t* __restrict__ slot,
                                    const int32_t* __restrict__ pos, const int32_t* __restrict__ back,
                                    float* __restrict__ out_f32, T* __restrict__ out) {
-  const int64_t t = blockIdx.x;
-  const int p = pos[t], b = back[t];
-  const float* st = state + (int64_t)slot[t] * (taps - 1) * C;
-  for (int64_t c = (int64_t)blockIdx.y * blockDim.x + threadIdx.x; c < C; c += (int64_t)gridDim.y * blockDim.x) {
-    const float ib = in_bias ? ldf(in_bias + c) : 0.f;
-    const float cur = x[t * ldx + c] + ib;
-    float acc = out_bias ? ldf(out_bias + c) : 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int delta = taps - 1 - j;
-      float v;
-      if (delta == 0) v = cur;
-      else if (delta <= b) v = x[(t - delta) * ldx + c] + ib;
-      else if (p - delta >= 0) v = st[(int64_t)(b - delta + taps - 1) * C + c];
-      else v = 0.f;
-      acc = fmaf(ldf(kern + c * taps + j), v, acc);
+  const int64_t c = (int64_t)blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int64_t t0 = (int64_t)blockIdx.x * kConvRows;
+  // xin[i] = input row t0 - (kMaxTaps - 1) + i, whichever sequence it belongs to (the rows decide below what they use)
+  float xin[kConvRows + kMaxTaps - 1];
+#pragma unroll
+  for (int i = 0; i < kConvRows + kMaxTaps - 1; ++i) {
+    const int64_t r = t0 - (kMaxTaps - 1) + i;
+    xin[i] = (r >= 0 && r < n && i >= kMaxTaps - taps) ? x[r * ldx + c] : 0.f;
+  }
+  int pb[kConvRows], pp[kConvRows], ps[kConvRows];
+#pragma unroll
+  for (int k = 0; k < kConvRows; ++k) {
+    const bool in = t0 + k < n;
+    pb[k] = in ? back[t0 + k] : 0, pp[k] = in ? pos[t0 + k] : 0, ps[k] = in ? slot[t0 + k] : 0;
+  }
+  const float ib = in_bias ? ldf(in_bias + c) : 0.f, ob = out_bias ? ldf(out_bias + c) : 0.f;
+  float wr[kMaxTaps];           // wr[delta] = the tap that meets the input delta rows back
+#pragma unroll
+  for (int dl = 0; dl < kMaxTaps; ++dl) wr[dl] = dl < taps ? ldf(kern + c * taps + (taps - 1 - dl)) : 0.f;
+#pragma unroll
+  for (int k = 0; k < kConvRows; ++k) {
+    const int64_t t = t0 + k;
+    if (t >= n) break;
+    const float cur = xin[k + kMaxTaps - 1] + ib;
+    float acc = fmaf(wr[0], cur, ob);
+#pragma unroll
+    for (int dl = 1; dl < kMaxTaps; ++dl) {
+      if (dl < taps) {
+        float v;
+        if (dl <= pb[k]) v = xin[k + kMaxTaps - 1 - dl] + ib;
+        else if (pp[k] - dl >= 0) v = state[((int64_t)ps[k] * (taps - 1) + (pb[k] - dl + taps - 1)) * C + c];
+        else v = 0.f;
+        acc = fmaf(wr[dl], v, acc);
+      }
     }
     if (residual) acc += cur;
     if (out_f32) out_f32[t * C + c] = acc;
@@ -64,16 +85,20 @@ struct MinGru {
   T* out;
   int64_t ld_out;
   struct Chan { float zb, xb; };
+  struct Raw { float z, x, g; };
   __device__ Chan channel(int64_t c) const { return {zb ? ldf(zb + c) : 0.f, xb ? ldf(xb + c) : 0.f}; }
-  __device__ void gates(const Chan& ch, int64_t t, int64_t c, float& a, float& b) const {
-    const float z = sigmoidf(zp[t * ld + c] + ch.zb), u = xp[t * ld + c] + ch.xb;
+  __device__ void load(const Chan&, int64_t t, int64_t c, bool rows, Raw& r) const {
+    r.z = zp[t * ld + c], r.x = xp[t * ld + c];
+    if (rows) r.g = gp[t * ld + c];
+  }
+  __device__ void gates(const Chan& ch, const Raw& r, float& a, float& b) const {
+    const float z = sigmoidf(r.z + ch.zb), u = r.x + ch.xb;
     const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
     a = 1.f - z;
     b = z * cand;
   }
-  __device__ void emit(const Chan&, int64_t t, int64_t c, float S) const {
-    const float g = gp[t * ld + c];
-    stf(out + t * ld_out + c, S * g * sigmoidf(g) * out_scale);
+  __device__ void emit(const Chan&, const Raw& r, int64_t t, int64_t c, float S) const {
+    stf(out + t * ld_out + c, S * r.g * sigmoidf(r.g) * out_scale);
   }
 };
 
@@ -100,15 +125,20 @@ struct RgLru {
     const int64_t blk = c / bw, o = c - blk * bw;
     return {ldf(rb + c), ldf(ib + c), sp, yb ? ldf(yb + c) : 0.f, blk * n * 2 * bw + o};
   }
-  __device__ void gates(const Chan& ch, int64_t t, int64_t c, float& a, float& b) const {
+  struct Raw { float r, i, u, y; };
+  __device__ void load(const Chan& ch, int64_t t, int64_t c, bool rows, Raw& v) const {
     const float* g = pre + ch.goff + t * 2 * bw;
-    const float r = sigmoidf(g[0] + ch.rb), i = sigmoidf(g[bw] + ch.ib);
+    v.r = g[0], v.i = g[bw], v.u = u[t * Rw + c];
+    if (rows) v.y = yp[t * ldy + c];
+  }
+  __device__ void gates(const Chan& ch, const Raw& v, float& a, float& b) const {
+    const float r = sigmoidf(v.r + ch.rb), i = sigmoidf(v.i + ch.ib);
     const float la = -decay * r * ch.sp;
     a = expf(la);
-    b = sqrtf(-expm1f(2.f * la)) * i * u[t * Rw + c];
+    b = sqrtf(-expm1f(2.f * la)) * i * v.u;
   }
-  __device__ void emit(const Chan& ch, int64_t t, int64_t c, float S) const {
-    stf(out + t * Rw + c, S * gelu_tanh(yp[t * ldy + c] + ch.yb));
+  __device__ void emit(const Chan& ch, const Raw& v, int64_t t, int64_t c, float S) const {
+    stf(out + t * Rw + c, S * gelu_tanh(v.y + ch.yb));
   }
 };
 
@@ -144,6 +174,27 @@ __device__ __forceinline__ void save_conv_rows(const ScanMeta& m, int64_t last, 
     if (k < taps - 1) st[(int64_t)k * Rw + c] = v[k];
 }
 
+// rows [first, first + count) of one channel: the raw inputs of kScanAhead rows are loaded before any is used (the
+// recurrence itself is a dependent chain; its loads are not)
+constexpr int kScanAhead = 4;
+template <bool kRows, typename F, typename Step>
+__device__ __forceinline__ void scan_rows(const F& f, const typename F::Chan& ch, int64_t first, int64_t count, int64_t c, Step step) {
+  for (int64_t t0 = first; t0 < first + count; t0 += kScanAhead) {
+    typename F::Raw raw[kScanAhead];
+#pragma unroll
+    for (int j = 0; j < kScanAhead; ++j)
+      if (t0 + j < first + count) f.load(ch, t0 + j, c, kRows, raw[j]);
+#pragma unroll
+    for (int j = 0; j < kScanAhead; ++j) {
+      if (t0 + j < first + count) {
+        float a, b;
+        f.gates(ch, raw[j], a, b);
+        step(t0 + j, raw[j], a, b);
+      }
+    }
+  }
+}
+
 // one launch: every tile is a whole segment.  grid (tiles, channel blocks)
 template <typename T, typename F>
 __global__ void __launch_bounds__(kScanThreads) scan_direct_kernel(F f, ScanMeta m, int64_t Rw) {
@@ -153,12 +204,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_direct_kernel(F f, ScanMeta
   float* st = m.state + (int64_t)m.slot[first] * Rw + c;
   float S = m.pos[first] > 0 ? *st : 0.f;
   const auto ch = f.channel(c);
-  for (int64_t t = first; t < first + count; ++t) {
-    float a, b;
-    f.gates(ch, t, c, a, b);
+  scan_rows<true>(f, ch, first, count, c, [&](int64_t t, const typename F::Raw& raw, float a, float b) {
     S = fmaf(a, S, b);
-    f.emit(ch, t, c, S);
-  }
+    f.emit(ch, raw, t, c, S);
+  });
   *st = S;
   if (m.conv_state) save_conv_rows<T>(m, first + count - 1, c, Rw);
 }
@@ -172,12 +221,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_reduce_kernel(F f, ScanMeta
   const int64_t first = m.tile_first[blockIdx.x], count = m.tile_count[blockIdx.x];
   const auto ch = f.channel(c);
   float A = 1.f, B = 0.f;
-  for (int64_t t = first; t < first + count; ++t) {
-    float a, b;
-    f.gates(ch, t, c, a, b);
+  scan_rows<false>(f, ch, first, count, c, [&](int64_t, const typename F::Raw&, float a, float b) {
     A *= a;
     B = fmaf(a, B, b);
-  }
+  });
   tA[(int64_t)blockIdx.x * Rw + c] = A;
   tB[(int64_t)blockIdx.x * Rw + c] = B;
 }
@@ -193,10 +240,18 @@ __global__ void __launch_bounds__(kScanThreads) scan_carry_kernel(ScanMeta m, in
   const int64_t first = m.tile_first[t0];
   float* st = m.state + (int64_t)m.slot[first] * Rw + c;
   float S = m.pos[first] > 0 ? *st : 0.f;
-  for (int i = t0; i < t0 + nt; ++i) {
-    const float A = tA[(int64_t)i * Rw + c], B = tB[(int64_t)i * Rw + c];
-    tB[(int64_t)i * Rw + c] = S;
-    S = fmaf(A, S, B);
+  for (int i0 = t0; i0 < t0 + nt; i0 += 8) {   // eight tiles' summaries in flight
+    float A[8], B[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i0 + j < t0 + nt) A[j] = tA[(int64_t)(i0 + j) * Rw + c], B[j] = tB[(int64_t)(i0 + j) * Rw + c];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (i0 + j < t0 + nt) {
+        tB[(int64_t)(i0 + j) * Rw + c] = S;
+        S = fmaf(A[j], S, B[j]);
+      }
+    }
   }
   *st = S;
   if (m.conv_state) {
@@ -213,12 +268,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(F f, ScanMeta 
   const int64_t first = m.tile_first[blockIdx.x], count = m.tile_count[blockIdx.x];
   const auto ch = f.channel(c);
   float S = tS[(int64_t)blockIdx.x * Rw + c];
-  for (int64_t t = first; t < first + count; ++t) {
-    float a, b;
-    f.gates(ch, t, c, a, b);
+  scan_rows<true>(f, ch, first, count, c, [&](int64_t t, const typename F::Raw& raw, float a, float b) {
     S = fmaf(a, S, b);
-    f.emit(ch, t, c, S);
-  }
+    f.emit(ch, raw, t, c, S);
+  });
 }
 
 template <typename T, typename F>
@@ -244,9 +297,9 @@ extern "C" int ao_lm_causal_conv(const float* x, int64_t ldx, const void* in_bia
                                  void* stream) {
   LM_CHECK_ARG(x && kernel && state && slot && pos && back && (out_f32 || out));
   LM_CHECK_ARG(n > 0 && channels > 0 && taps >= 2 && taps <= kMaxTaps && ldx >= channels);
-  const unsigned cb = (unsigned)((channels + 255) / 256);
-  LM_DISPATCH(dt, causal_conv_kernel<T><<<dim3((unsigned)n, cb), 256, 0, lm_stream(stream)>>>(
-                      x, ldx, static_cast<const T*>(in_bias), channels, taps, static_cast<const T*>(kernel),
+  const unsigned cb = (unsigned)((channels + 127) / 128);
+  LM_DISPATCH(dt, causal_conv_kernel<T><<<dim3((unsigned)((n + kConvRows - 1) / kConvRows), cb), 128, 0, lm_stream(stream)>>>(
+                      x, ldx, static_cast<const T*>(in_bias), n, channels, taps, static_cast<const T*>(kernel),
                       static_cast<const T*>(out_bias), residual, state, slot, pos, back, out_f32, static_cast<T*>(out)));
   return lm_launch_status();
 }

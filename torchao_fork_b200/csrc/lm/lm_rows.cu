@@ -214,6 +214,12 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int6
 
 }  // namespace
 
+int g_lm_last_cuda_error = 0;
+
+extern "C" const char* ao_lm_last_cuda_error(void) {
+  return g_lm_last_cuda_error ? cudaGetErrorString((cudaError_t)g_lm_last_cuda_error) : "";
+}
+
 extern "C" int ao_lm_abi_version(void) { return 1; }
 
 extern "C" int ao_lm_embed(const void* table, int dt, const int64_t* tok, int64_t n, int64_t width, float* x, void* stream) {

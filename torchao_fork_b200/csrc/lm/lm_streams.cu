@@ -19,7 +19,7 @@ inline unsigned row_threads(int64_t rows, int64_t width) {
 }
 
 template <typename T>
-__global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int64_t* __restrict__ tok,
+__global__ void __launch_bounds__(1024) embed_sinusoid_kernel(const T* __restrict__ table, const int64_t* __restrict__ tok,
                                       const int32_t* __restrict__ pos, int64_t W, float scale,
                                       const double* __restrict__ freq, int S, float* __restrict__ x) {
   const int64_t t = blockIdx.x;
@@ -37,7 +37,7 @@ __global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int64_t
 
 // u = sum_s cin[s] x_s (cin == null: every coefficient 1);  out = u / sqrt(mean(u^2) + eps) * (offset + weight)
 template <typename T>
-__global__ void streams_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, int S, int64_t W,
+__global__ void __launch_bounds__(1024) streams_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, int S, int64_t W,
                                     const T* __restrict__ cin, const T* __restrict__ weight, float offset, float eps,
                                     float* __restrict__ out_f32, T* __restrict__ out) {
   extern __shared__ float u[];          // [W]
@@ -69,7 +69,7 @@ __global__ void streams_norm_kernel(const float* __restrict__ x, const int32_t* 
 // The last row of every sequence in the step (ahead == 0) also shifts the rows of conv_in into the sequence's
 // convolution memory: state[slot][k] = input at position p - (taps - 2 - k).
 template <typename T, typename TY>
-__global__ void streams_update_kernel(float* __restrict__ x, const TY* __restrict__ y, int S, int64_t W,
+__global__ void __launch_bounds__(1024) streams_update_kernel(float* __restrict__ x, const TY* __restrict__ y, int S, int64_t W,
                                       const T* __restrict__ mix, const T* __restrict__ cout, const float* __restrict__ conv_in,
                                       float* __restrict__ conv_state, int taps, const int32_t* __restrict__ slot,
                                       const int32_t* __restrict__ back, const int32_t* __restrict__ ahead) {
