@@ -46,6 +46,23 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
   float wr[kMaxTaps];           // wr[delta] = the tap that meets the input delta rows back
 #pragma unroll
   for (int dl = 0; dl < kMaxTaps; ++dl) wr[dl] = dl < taps ? ldf(kern + c * taps + (taps - 1 - dl)) : 0.f;
+  // a tile whose rows all have taps - 1 rows of their own segment in front of them needs neither memory nor zeros
+  bool interior = t0 + kConvRows <= n;
+#pragma unroll
+  for (int k = 0; k < kConvRows; ++k) interior = interior && pb[k] >= taps - 1;
+  if (interior) {   // uniform over the CTA
+#pragma unroll
+    for (int k = 0; k < kConvRows; ++k) {
+      const float cur = xin[k + kMaxTaps - 1] + ib;
+      float acc = fmaf(wr[0], cur, ob);
+#pragma unroll
+      for (int dl = 1; dl < kMaxTaps; ++dl) acc = fmaf(wr[dl], xin[k + kMaxTaps - 1 - dl] + ib, acc);   // wr = 0 past the taps
+      if (residual) acc += cur;
+      if (out_f32) out_f32[(t0 + k) * C + c] = acc;
+      if (out) stf(out + (t0 + k) * C + c, acc);
+    }
+    return;
+  }
 #pragma unroll
   for (int k = 0; k < kConvRows; ++k) {
     const int64_t t = t0 + k;
@@ -69,10 +86,22 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, int64_t ldx, con
 }
 
 // ---------------------------------------------------------------------------------------------- gated recurrences
-__device__ __forceinline__ float sigmoidf(float v) { return 1.f / (1.f + expf(-v)); }
-__device__ __forceinline__ float gelu_tanh(float z) {
-  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+// kFast (bf16 storage): one hardware exponential and an approximate reciprocal per function, errors of a few 1e-7 —
+// three orders of magnitude below what bf16 operands leave in the inputs.  fp32 storage keeps the library functions.
+template <bool kFast>
+__device__ __forceinline__ float sigmoid_(float v) {
+  return kFast ? __fdividef(1.f, 1.f + __expf(-v)) : 1.f / (1.f + expf(-v));
 }
+template <bool kFast>
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  const float x = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  const float th = kFast ? 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f) : tanhf(x);
+  return 0.5f * z * (1.f + th);
+}
+template <typename T>
+struct FastMath { static constexpr bool value = true; };
+template <>
+struct FastMath<float> { static constexpr bool value = false; };
 
 // minimal GRU: z = sigmoid(zp + zb), u = xp + xb, candidate = u + 1/2 (u >= 0) | sigmoid(u);  a = 1 - z, b = z * candidate;
 // row result = S * silu(gp) * out_scale
@@ -84,6 +113,7 @@ struct MinGru {
   float out_scale;
   T* out;
   int64_t ld_out;
+  static constexpr bool kFast = FastMath<T>::value;
   struct Chan { float zb, xb; };
   struct Raw { float z, x, g; };
   __device__ Chan channel(int64_t c) const { return {zb ? ldf(zb + c) : 0.f, xb ? ldf(xb + c) : 0.f}; }
@@ -92,13 +122,13 @@ struct MinGru {
     if (rows) r.g = gp[t * ld + c];
   }
   __device__ void gates(const Chan& ch, const Raw& r, float& a, float& b) const {
-    const float z = sigmoidf(r.z + ch.zb), u = r.x + ch.xb;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
+    const float z = sigmoid_<kFast>(r.z + ch.zb), u = r.x + ch.xb;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_<kFast>(u);
     a = 1.f - z;
     b = z * cand;
   }
   __device__ void emit(const Chan&, const Raw& r, int64_t t, int64_t c, float S) const {
-    stf(out + t * ld_out + c, S * r.g * sigmoidf(r.g) * out_scale);
+    stf(out + t * ld_out + c, S * r.g * sigmoid_<kFast>(r.g) * out_scale);
   }
 };
 
@@ -118,6 +148,7 @@ struct RgLru {
   const T* yb;
   T* out;
   int64_t Rw;
+  static constexpr bool kFast = FastMath<T>::value;
   struct Chan { float rb, ib, sp, yb; int64_t goff; };
   __device__ Chan channel(int64_t c) const {
     const float l = ldf(lam + c);
@@ -132,13 +163,18 @@ struct RgLru {
     if (rows) v.y = yp[t * ldy + c];
   }
   __device__ void gates(const Chan& ch, const Raw& v, float& a, float& b) const {
-    const float r = sigmoidf(v.r + ch.rb), i = sigmoidf(v.i + ch.ib);
+    const float r = sigmoid_<kFast>(v.r + ch.rb), i = sigmoid_<kFast>(v.i + ch.ib);
     const float la = -decay * r * ch.sp;
-    a = expf(la);
-    b = sqrtf(-expm1f(2.f * la)) * i * v.u;
+    if (kFast) {
+      a = __expf(la);
+      b = sqrtf(fmaxf(1.f - a * a, 0.f)) * i * v.u;
+    } else {
+      a = expf(la);
+      b = sqrtf(-expm1f(2.f * la)) * i * v.u;
+    }
   }
   __device__ void emit(const Chan& ch, const Raw& v, int64_t t, int64_t c, float S) const {
-    stf(out + t * Rw + c, S * gelu_tanh(v.y + ch.yb));
+    stf(out + t * Rw + c, S * gelu_tanh_<kFast>(v.y + ch.yb));
   }
 };
 
