@@ -158,7 +158,8 @@ AO_B200_API int ao_lm_gelu_glu(const void* gu, int dt, int64_t n, int64_t ff, vo
 /* Causal convolution over time per channel: v(t) = x[t][c] + in_bias[c];
  * y[t][c] = (residual ? v(t) : 0) + out_bias[c] + sum_j kernel[c][j] * v(t - (taps - 1 - j)).  Inputs in front of the
  * step come from state[slot][taps - 1][channels] (oldest first, bias included), inputs in front of position 0 are zero.
- * The kernel does not write the state: ao_lm_streams_update / ao_lm_rglru_scan do, after every reader has run. */
+ * The kernel does not write the state: ao_lm_streams_update / ao_lm_rglru_scan do, after every reader has run.
+ * taps == 1 reads no state (pass any valid pointer). */
 AO_B200_API int ao_lm_causal_conv(const float* x, int64_t ldx, const void* in_bias, int64_t n, int64_t channels, int taps,
                                   const void* kernel, const void* out_bias, int dt, int residual, const float* state,
                                   const int32_t* slot, const int32_t* pos, const int32_t* back, float* out_f32, void* out,

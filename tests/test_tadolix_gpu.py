@@ -419,10 +419,10 @@ def _plain():
 
 
 def _ones():
-    """Sizes that make things equal or one: one stream WITH weights, two taps, a loop that runs once, chunks of one
-    position, blocks of one channel, one head."""
+    """Sizes that make things equal or one: one stream WITH weights, convolutions of one tap, a loop that runs once,
+    chunks of one position, blocks of one channel, one head."""
     return O.make_config([O.attention_layer(heads=1, kv_heads=1, dim=4, vdim=4, chunk=1, rows=2, bias_max=2, right=16),
-                          O.recurrent_layer(16, 16, 2)], width=16, streams=1, taps=2, loop=(0, 2, 1))
+                          O.recurrent_layer(16, 16, 1), O.recurrent_layer(16, 1, 2)], width=16, streams=1, taps=1, loop=(0, 3, 1))
 
 
 def _tensor():

@@ -156,13 +156,14 @@ class RecurrentState(nn.Module):
 
 
 class ConvState(nn.Module):
-    """The last taps - 1 inputs of a causal convolution over time, fp32 [slots][taps - 1][channels], oldest first."""
+    """The last taps - 1 inputs of a causal convolution over time, fp32 [slots][taps - 1][channels], oldest first (a
+    one-tap convolution remembers nothing: it keeps one unused row so that the buffer exists)."""
 
     def __init__(self, n_slots, taps, channels, device=None):
         super().__init__()
-        assert taps >= 2
+        assert taps >= 1
         self.taps = taps
-        self.register_buffer("x", torch.zeros(n_slots, taps - 1, channels, dtype=torch.float32, device=device))
+        self.register_buffer("x", torch.zeros(n_slots, max(1, taps - 1), channels, dtype=torch.float32, device=device))
 
     def grow(self, n_slots):
         self.x = _grown(self.x, n_slots)

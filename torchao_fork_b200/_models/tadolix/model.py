@@ -108,7 +108,7 @@ class TadolixArgs:
                 mixer = ParallelArgs(left, int(m["right"]["width"]), float(m["left_scale"]), float(m["right_scale"]))
             elif kind == "rglru":
                 mixer = RgLruArgs(int(m["width"]), int(m["blocks"]), int(m["conv"]))
-                assert mixer.width % mixer.blocks == 0 and 2 <= mixer.conv <= MAX_TAPS, f"layer {i}: {mixer}"
+                assert mixer.width % mixer.blocks == 0 and 1 <= mixer.conv <= MAX_TAPS, f"layer {i}: {mixer}"
             else:
                 raise NotImplementedError(f"layer {i}: mixer type {kind!r}")
             f = lay.get("mlp")
@@ -121,7 +121,7 @@ class TadolixArgs:
             assert 0 <= loop[0] <= loop[1] <= len(layers) and loop[2] >= 1, f"loop {loop}"
         streams = int(cfg.get("streams") or 0)
         taps = int((cfg.get("canon") or {}).get("taps") or 0)
-        assert streams <= MAX_STREAMS and taps <= MAX_TAPS and taps != 1
+        assert streams <= MAX_STREAMS and taps <= MAX_TAPS
         return cls(vocab_size=int(cfg["vocab"]), width=int(cfg["width"]), norm_eps=float(cfg["norm"]["eps"]),
                    embedding_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)), streams=streams, canon_taps=taps,
                    loop=loop, layers=layers)

@@ -248,8 +248,8 @@ class StepEngine:
             launches += k + 1
             _lib.lm_check(L.ao_lm_streams_update(
                 _p(x), _p(y), _lib.DT_F32, n, S, W, _p(hc[2]) if hc else None, _p(hc[1]) if hc else None, dt,
-                _p(hn) if taps else None, _p(rs.canon.x) if taps else None, taps, _p(meta.slot), _p(meta.back), _p(meta.ahead),
-                st), "streams_update")
+                _p(hn) if taps > 1 else None, _p(rs.canon.x) if taps > 1 else None, taps, _p(meta.slot), _p(meta.back),
+                _p(meta.ahead), st), "streams_update")
             # ---- feed-forward sublayer
             if la.ff:
                 hc = lay.hc[1]
@@ -343,7 +343,8 @@ class StepEngine:
         ws = self._scan_ws(meta, Rw)
         _lib.lm_check(L.ao_lm_rglru_scan(
             _p(gates), n, bw, _p(lay.ra_b), _p(lay.ri_b), _p(lay.lam), RGLRU_DECAY, _p(u), _p(proj), 2 * Rw, _p(lay.y_b), dt, Rw,
-            _p(rs.rec.s), proj.data_ptr() + 4 * Rw, 2 * Rw, _p(lay.x_b), _p(rs.conv.x), mx.conv, _p(meta.slot), _p(meta.pos),
+            _p(rs.rec.s), proj.data_ptr() + 4 * Rw, 2 * Rw, _p(lay.x_b), _p(rs.conv.x) if mx.conv > 1 else None, mx.conv,
+            _p(meta.slot), _p(meta.pos),
             _p(meta.back), _p(sf), _p(sc), snt, _p(seg0), _p(segn), ns, _p(ws), _p(out), st), "rglru_scan")
         y = self._mm_f32(out, lay.w_out)
         return y, 5 + (2 if seg0 is not None else 0)

@@ -332,7 +332,7 @@ extern "C" int ao_lm_causal_conv(const float* x, int64_t ldx, const void* in_bia
                                  const int32_t* slot, const int32_t* pos, const int32_t* back, float* out_f32, void* out,
                                  void* stream) {
   LM_CHECK_ARG(x && kernel && state && slot && pos && back && (out_f32 || out));
-  LM_CHECK_ARG(n > 0 && channels > 0 && taps >= 2 && taps <= kMaxTaps && ldx >= channels);
+  LM_CHECK_ARG(n > 0 && channels > 0 && taps >= 1 && taps <= kMaxTaps && ldx >= channels);
   const unsigned cb = (unsigned)((channels + 127) / 128);
   LM_DISPATCH(dt, causal_conv_kernel<T><<<dim3((unsigned)((n + kConvRows - 1) / kConvRows), cb), 128, 0, lm_stream(stream)>>>(
                       x, ldx, static_cast<const T*>(in_bias), n, channels, taps, static_cast<const T*>(kernel),

@@ -115,6 +115,129 @@ __global__ void __launch_bounds__(1024) streams_update_kernel(float* __restrict_
   }
 }
 
+
+// ---- the same two kernels for widths that are multiples of 4: 16-byte loads and stores, the stream count a
+// compile-time constant (no predicated loops)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xFFFF0000u));
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float4& v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename T, int S>
+__global__ void __launch_bounds__(512) streams_norm_vec_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                                                                int64_t W, const T* __restrict__ cin, const T* __restrict__ weight,
+                                                                float offset, float eps, float* __restrict__ out_f32,
+                                                                T* __restrict__ out) {
+  extern __shared__ __align__(16) float u[];   // [W]
+  __shared__ float scratch[33];
+  const int64_t i = blockIdx.x;
+  const float* xr = x + (rows ? (int64_t)rows[i] : i) * S * W;
+  float c[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) c[s] = cin ? ldf(cin + s) : 1.f;
+  float ss = 0.f;
+  for (int64_t w = (int64_t)threadIdx.x * 4; w < W; w += (int64_t)blockDim.x * 4) {
+    float4 v[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) v[s] = ld4(xr + s * W + w);
+    float4 a = make_float4(c[0] * v[0].x, c[0] * v[0].y, c[0] * v[0].z, c[0] * v[0].w);
+#pragma unroll
+    for (int s = 1; s < S; ++s) {
+      a.x = fmaf(c[s], v[s].x, a.x), a.y = fmaf(c[s], v[s].y, a.y), a.z = fmaf(c[s], v[s].z, a.z), a.w = fmaf(c[s], v[s].w, a.w);
+    }
+    st4(u + w, a);
+    ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+  }
+  ss = block_sum(ss, scratch);
+  const float k = 1.f / sqrtf(ss / (float)W + eps);
+  for (int64_t w = (int64_t)threadIdx.x * 4; w < W; w += (int64_t)blockDim.x * 4) {
+    const float4 a = ld4(u + w), g = ld4(weight + w);
+    const float4 v = make_float4(a.x * k * (offset + g.x), a.y * k * (offset + g.y), a.z * k * (offset + g.z), a.w * k * (offset + g.w));
+    if (out_f32) st4(out_f32 + i * W + w, v);
+    if (out) st4(out + i * W + w, v);
+  }
+}
+
+template <typename T, typename TY, int S>
+__global__ void __launch_bounds__(512) streams_update_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, int64_t W,
+                                                                  const T* __restrict__ mix, const T* __restrict__ cout) {
+  float m[S][S], co[S];
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    co[s] = cout ? ldf(cout + s) : 1.f;
+#pragma unroll
+    for (int d = 0; d < S; ++d) m[s][d] = mix ? ldf(mix + s * S + d) : (s == d ? 1.f : 0.f);
+  }
+  const int64_t t = blockIdx.x;
+  float* xr = x + t * S * W;
+  const TY* yr = y + t * W;
+  for (int64_t w = (int64_t)threadIdx.x * 4; w < W; w += (int64_t)blockDim.x * 4) {
+    float4 v[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) v[s] = ld4(xr + s * W + w);
+    const float4 yv = ld4(yr + w);
+#pragma unroll
+    for (int d = 0; d < S; ++d) {
+      float4 a = make_float4(co[d] * yv.x, co[d] * yv.y, co[d] * yv.z, co[d] * yv.w);
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+        a.x = fmaf(m[s][d], v[s].x, a.x), a.y = fmaf(m[s][d], v[s].y, a.y), a.z = fmaf(m[s][d], v[s].z, a.z),
+        a.w = fmaf(m[s][d], v[s].w, a.w);
+      }
+      st4(xr + d * W + w, a);
+    }
+  }
+}
+
+// the convolution memory alone (what streams_update_kernel does for rows with ahead == 0), for the vector path
+__global__ void conv_memory_kernel(const float* __restrict__ conv_in, float* __restrict__ conv_state, int64_t W, int taps,
+                                   const int32_t* __restrict__ slot, const int32_t* __restrict__ back,
+                                   const int32_t* __restrict__ ahead) {
+  const int64_t t = blockIdx.x;
+  if (ahead[t] != 0) return;
+  const int b = back[t];
+  float* st = conv_state + (int64_t)slot[t] * (taps - 1) * W;
+  for (int64_t w = threadIdx.x; w < W; w += blockDim.x) {
+    float v[kMaxTaps];
+#pragma unroll
+    for (int k = 0; k < kMaxTaps - 1; ++k) {
+      if (k < taps - 1) {
+        const int delta = taps - 2 - k;
+        v[k] = delta <= b ? conv_in[(t - delta) * W + w] : st[(int64_t)(b - delta + taps - 1) * W + w];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxTaps - 1; ++k)
+      if (k < taps - 1) st[(int64_t)k * W + w] = v[k];
+  }
+}
+
+inline unsigned vec_threads(int64_t rows, int64_t width) {
+  unsigned t = 128;
+  const unsigned cap = rows >= 128 ? 256 : 512;
+  while (t < cap && (int64_t)t * 4 < width) t *= 2;
+  return t;
+}
+
+#define LM_STREAMS_SWITCH(S_, ...)          \
+  switch (S_) {                             \
+    case 1: { constexpr int S = 1; __VA_ARGS__; } break; \
+    case 2: { constexpr int S = 2; __VA_ARGS__; } break; \
+    case 3: { constexpr int S = 3; __VA_ARGS__; } break; \
+    case 4: { constexpr int S = 4; __VA_ARGS__; } break; \
+    case 5: { constexpr int S = 5; __VA_ARGS__; } break; \
+    case 6: { constexpr int S = 6; __VA_ARGS__; } break; \
+    case 7: { constexpr int S = 7; __VA_ARGS__; } break; \
+    default: { constexpr int S = 8; __VA_ARGS__; } break; \
+  }
+
 __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -144,6 +267,14 @@ extern "C" int ao_lm_streams_norm(const float* x, const int32_t* rows, int64_t m
   LM_CHECK_ARG(x && weight && (out_f32 || out) && m > 0 && width > 0 && n_streams >= 1 && n_streams <= kMaxStreams);
   LM_CHECK_ARG(width * 4 <= 160 * 1024);
   const size_t smem = (size_t)width * 4;
+  const bool vec = width % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 8 == 0 &&
+                   reinterpret_cast<uintptr_t>(out_f32) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0 && smem <= 40 * 1024;
+  if (vec) {
+    LM_DISPATCH(dt, LM_STREAMS_SWITCH(n_streams, streams_norm_vec_kernel<T, S><<<(unsigned)m, vec_threads(m, width), smem, lm_stream(stream)>>>(
+                        x, rows, width, static_cast<const T*>(coef_in), static_cast<const T*>(weight), weight_offset, eps, out_f32,
+                        static_cast<T*>(out))));
+    return lm_launch_status();
+  }
   LM_DISPATCH(dt, {
     auto kern = streams_norm_kernel<T>;
     if (smem > 40 * 1024) {
@@ -167,6 +298,20 @@ extern "C" int ao_lm_streams_update(float* x, const void* y, int y_dt, int64_t n
   LM_CHECK_ARG(!conv_state || (conv_in && slot && back && ahead && taps >= 2 && taps <= kMaxTaps));
   const cudaStream_t st = lm_stream(stream);
   const unsigned th = row_threads(n, width);
+  if (width % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0 &&
+      (y_dt == AO_LM_F32 || dt == AO_LM_BF16)) {
+    const unsigned vt = vec_threads(n, width);
+    if (y_dt == AO_LM_F32) {
+      LM_DISPATCH(dt, LM_STREAMS_SWITCH(n_streams, streams_update_vec_kernel<T, float, S><<<(unsigned)n, vt, 0, st>>>(
+                          x, static_cast<const float*>(y), width, static_cast<const T*>(mix), static_cast<const T*>(coef_out))));
+    } else {
+      using T = __nv_bfloat16;
+      LM_STREAMS_SWITCH(n_streams, streams_update_vec_kernel<T, T, S><<<(unsigned)n, vt, 0, st>>>(
+                            x, static_cast<const T*>(y), width, static_cast<const T*>(mix), static_cast<const T*>(coef_out)));
+    }
+    if (conv_state) conv_memory_kernel<<<(unsigned)n, 256, 0, st>>>(conv_in, conv_state, width, taps, slot, back, ahead);
+    return lm_launch_status();
+  }
   if (y_dt == AO_LM_F32) {
     LM_DISPATCH(dt, streams_update_kernel<T, float><<<(unsigned)n, th, 0, st>>>(
                         x, static_cast<const float*>(y), n_streams, width, static_cast<const T*>(mix),
