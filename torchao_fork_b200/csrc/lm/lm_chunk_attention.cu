@@ -207,20 +207,38 @@ __global__ void __launch_bounds__(kWarps * 32) chunk_attention_merge_kernel(Chun
   for (int pr = warp; pr < npairs; pr += kWarps) {
     const float* w0 = a.ws + ((((int64_t)tile * a.G + g) * a.n_split) * (kWarps * kPairSlots) + pr) * (dv + 2);
     const int64_t stride = (int64_t)(kWarps * kPairSlots) * (dv + 2);
-    float top = -INFINITY;
-    for (int z = 0; z < a.n_split; ++z) top = fmaxf(top, w0[z * stride]);
-    float den = 0.f, o[kMaxDvLane];
+    // lane z (and z + 32) holds share z's maximum and denominator: all shares are read at once
+    float mz[2], dz[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int z = lane + 32 * i;
+      mz[i] = z < a.n_split ? w0[z * stride] : -INFINITY;
+      dz[i] = z < a.n_split ? w0[z * stride + 1] : 0.f;
+    }
+    const float top = warp_max(fmaxf(mz[0], mz[1]));
+    float fz[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) fz[i] = mz[i] == -INFINITY ? 0.f : expf(mz[i] - top);
+    const float den = warp_sum(dz[0] * fz[0] + dz[1] * fz[1]);
+    float o[kMaxDvLane];
 #pragma unroll
     for (int e = 0; e < kMaxDvLane; ++e) o[e] = 0.f;
-    for (int z = 0; z < a.n_split; ++z) {
-      const float* w = w0 + z * stride;
-      if (w[0] == -INFINITY) continue;
-      const float f = expf(w[0] - top);
-      den = fmaf(w[1], f, den);
+    for (int z0 = 0; z0 < a.n_split; z0 += 8) {   // eight shares' sums in flight
+      float v[8][kMaxDvLane];
 #pragma unroll
-      for (int e = 0; e < kMaxDvLane; ++e) {
-        const int c = lane + 32 * e;
-        if (c < dv) o[e] = fmaf(w[2 + c], f, o[e]);
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < kMaxDvLane; ++e) {
+          const int c = lane + 32 * e;
+          v[j][e] = (z0 + j < a.n_split && c < dv) ? w0[(z0 + j) * stride + 2 + c] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int z = z0 + j;   // z0 is a multiple of 8: all eight sit in the same half
+        const float f = __shfl_sync(0xffffffffu, z < 32 ? fz[0] : fz[1], z & 31);
+#pragma unroll
+        for (int e = 0; e < kMaxDvLane; ++e) o[e] = fmaf(v[j][e], f, o[e]);
       }
     }
     const int r = pr / rep, qh = g * rep + pr % rep;

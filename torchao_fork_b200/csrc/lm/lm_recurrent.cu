@@ -276,13 +276,13 @@ __global__ void __launch_bounds__(kScanThreads) scan_carry_kernel(ScanMeta m, in
   const int64_t first = m.tile_first[t0];
   float* st = m.state + (int64_t)m.slot[first] * Rw + c;
   float S = m.pos[first] > 0 ? *st : 0.f;
-  for (int i0 = t0; i0 < t0 + nt; i0 += 8) {   // eight tiles' summaries in flight
-    float A[8], B[8];
+  for (int i0 = t0; i0 < t0 + nt; i0 += 16) {   // sixteen tiles' summaries in flight
+    float A[16], B[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < 16; ++j)
       if (i0 + j < t0 + nt) A[j] = tA[(int64_t)(i0 + j) * Rw + c], B[j] = tB[(int64_t)(i0 + j) * Rw + c];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 16; ++j) {
       if (i0 + j < t0 + nt) {
         tB[(int64_t)(i0 + j) * Rw + c] = S;
         S = fmaf(A[j], S, B[j]);
