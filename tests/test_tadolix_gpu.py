@@ -319,7 +319,7 @@ ATTN_SHAPES = [dict(heads=6, kv_heads=2, dim=8, vdim=12, chunk=8, rows=6, bias_m
                dict(heads=2, kv_heads=2, dim=16, vdim=16, chunk=5, rows=7, bias_max=4),
                dict(heads=4, kv_heads=1, dim=32, vdim=64, chunk=16, rows=16, bias_max=12),
                dict(heads=3, kv_heads=3, dim=5, vdim=3, chunk=1, rows=2, bias_max=3),
-               dict(heads=8, kv_heads=2, dim=64, vdim=64, chunk=64, rows=32, bias_max=128),
+               dict(heads=8, kv_heads=4, dim=64, vdim=48, chunk=80, rows=32, bias_max=128),
                dict(heads=2, kv_heads=1, dim=128, vdim=128, chunk=96, rows=8, bias_max=50)]
 
 

@@ -56,7 +56,7 @@ def test_registry_knows_the_family_and_its_names(tmp_path):
     assert "_rel_rows" not in read_config(str(tmp_path))["layers"][1]["mixer"]
 
 
-@pytest.mark.parametrize("B,D", [(16, 120), (6, 20), (7, 33), (2, 9), (32, 128), (16, 128)])
+@pytest.mark.parametrize("B,D", [(16, 100), (6, 20), (7, 33), (2, 9), (32, 128), (16, 128)])
 def test_distance_bias_table_is_the_bucket_function(B, D):
     rel = torch.arange(B * 3, dtype=torch.float32).view(B, 3)
     n = 3 * D

@@ -171,7 +171,7 @@ def _pattern(n_layer, width, heads, kv_heads, dim, chunk, ff, vocab, streams=4, 
     for i in range(n_layer):
         if i % 3 == 0:
             a = ChunkAttentionArgs(heads, kv_heads, dim, dim, chunk, 2 * chunk, 1.0 / math.sqrt(dim) * 4.0, 30.0)
-            layers.append(LayerArgs("parallel", ParallelArgs(a, width, 0.8, 0.9), ff))
+            layers.append(LayerArgs("parallel", ParallelArgs(a, width, 0.7, 1.1), ff))
         else:
             layers.append(LayerArgs("rglru", RgLruArgs(width, blocks or max(1, width // 256), 4), ff))
     return TadolixArgs(vocab, width, 1e-6, 8.0, streams, taps, None, layers)
