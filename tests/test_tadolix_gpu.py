@@ -431,7 +431,14 @@ def _tensor():
                           O.recurrent_layer(64, 2, 4)], width=64, vocab=97, streams=2, taps=4, loop=(0, 2, 3))
 
 
-CONFIGS = {"mixed": _mixed, "plain": _plain, "ones": _ones, "tensor": _tensor}
+def _odd():
+    """Nothing is a multiple of 2, 4 or 16: width, vocabulary, head sizes, recurrence widths, feed-forward, chunk."""
+    return O.make_config([O.attention_layer(heads=3, kv_heads=3, dim=7, vdim=5, chunk=9, rows=5, bias_max=7, right=21, ff=25),
+                          O.recurrent_layer(21, 3, 3, ff=0), O.attention_layer(heads=5, kv_heads=1, dim=3, vdim=9, chunk=11, rows=9, right=13, ff=0)],
+                         width=35, vocab=53, streams=5, taps=5, loop=(1, 3, 3))
+
+
+CONFIGS = {"mixed": _mixed, "plain": _plain, "ones": _ones, "tensor": _tensor, "odd": _odd}
 
 
 @pytest.mark.parametrize("name", list(CONFIGS))
@@ -447,8 +454,9 @@ def test_whole_prompt_and_every_layer_run_against_oracle(name, dtype):
     assert _err(logits, ref) <= tol
     if dtype == torch.float32:
         assert sums.shape == ref_layers.shape
-        for r in range(sums.shape[0]):
-            assert torch.allclose(sums[r].double().cpu(), ref_layers[r], rtol=1e-4, atol=1e-4), r
+        for r in range(sums.shape[0]):     # small coordinates beside large ones: the bound follows the run's largest value
+            scale = float(ref_layers[r].abs().max())
+            assert torch.allclose(sums[r].double().cpu(), ref_layers[r], rtol=1e-4, atol=1e-5 * max(1.0, scale)), r
 
 
 @pytest.mark.parametrize("name", list(CONFIGS))
